@@ -5,7 +5,8 @@ state of fixed size.
 Runs with the same needs (KV heads, head size, all keys or a window of them) form
 a group with storage of its own: K and V of shape
 [runs of the group, pages, kv heads, PAGE positions, head_dim], so that one page of
-one KV head is a contiguous [PAGE, head_dim] tile.  A sequence's positions map to
+one KV head is a contiguous [PAGE, head_dim] tile (values may have a size of their own,
+or be left out where a mixer finds them in its key rows).  A sequence's positions map to
 pages through its page table; a windowed group keeps only a ring of pages per
 sequence (position p lives in table entry (p // PAGE) % ring_pages), sized so that
 every key a step can still need is resident: window + the longest step - 1
@@ -30,6 +31,8 @@ class KVSpec:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None        # None: all keys; W: the last W positions
+    v_dim: Optional[int] = None         # entries of a value: None as head_dim; 0: no values are kept (a mixer
+                                        # whose values are part of its key rows)
 
 
 @dataclass
@@ -92,9 +95,10 @@ class Cache:
         if device is not None:
             import torch
             for g in self.groups:
-                shape = (len(g.runs), g.n_pages, g.spec.n_kv_heads, PAGE, g.spec.head_dim)
-                g.k = torch.empty(shape, dtype=dtype, device=device)
-                g.v = torch.empty(shape, dtype=dtype, device=device)
+                shape = (len(g.runs), g.n_pages, g.spec.n_kv_heads, PAGE)
+                g.k = torch.empty(shape + (g.spec.head_dim,), dtype=dtype, device=device)
+                v_dim = g.spec.head_dim if g.spec.v_dim is None else g.spec.v_dim
+                g.v = torch.empty(shape + (v_dim,), dtype=dtype, device=device) if v_dim else None
             # all fixed-size state lies in one arena, region after region (each [slots, row]), so that one
             # kernel launch zeroes a slot's row of every state when the slot opens
             regions, off = [], 0

@@ -1,5 +1,5 @@
 """The one registry from an architecture's name to its configuration class and its
-model builder.  config.json's `architectures[0]` (or `model_type`) picks the entry.
+model builder.  config.json's `architectures[0]` (or `architecture`, or `model_type`) picks the entry.
 
 The reference has no registry: one model struct serves every
 `general.architecture` string and only prints it (src/main.rs:72-73,
@@ -43,10 +43,11 @@ def registered_architectures():
 
 def resolve_architecture(raw: Dict[str, Any]) -> Architecture:
     names = list(raw.get("architectures") or [])
-    if raw.get("model_type"):
-        names.append(raw["model_type"])
+    for key in ("architecture", "model_type"):
+        if isinstance(raw.get(key), str):
+            names.append(raw[key])
     if not names:
-        raise ConfigError("config.json names no architecture (keys 'architectures' or 'model_type')")
+        raise ConfigError("config.json names no architecture (keys 'architectures', 'architecture' or 'model_type')")
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]

@@ -28,10 +28,11 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """A block and its parts.  `block` names the arrangement (how norms, mixer and
-    feed-forward are wired around the residual stream)."""
+    feed-forward are wired around the residual stream).  feed_forward None: the layer is its
+    mixer alone."""
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: Dict[str, PartSpec]
     position: Optional[PartSpec] = None
 

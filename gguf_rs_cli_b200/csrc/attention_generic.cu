@@ -12,24 +12,27 @@
 
 #include "common.cuh"
 
-constexpr int AG_MAX_HD = 256;
+constexpr int AG_MAX_HD = 640;
 constexpr int AG_WARPS = 4;
 
-template <typename TC>
+// hd: entries of a query and of a key; hdv: entries of a value (and of a head's result); a value row starts
+// every v_row entries of the value storage, which lets the values be the first hdv entries of the key rows
+// themselves (attention over one shared latent row per position).  MAX_HD bounds both sizes.
+template <typename TC, int MAX_HD>
 __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     const void* __restrict__ q, int q_dtype, long long ldq, void* __restrict__ out, int out_dtype, long long ldo,
-    int nh, int nkv, int hd, const int* __restrict__ seq_of, const int* __restrict__ pos,
+    int nh, int nkv, int hd, int hdv, int v_row, const int* __restrict__ seq_of, const int* __restrict__ pos,
     const int* __restrict__ table, int table_width, int ring_pages, const TC* __restrict__ kc,
     const TC* __restrict__ vc, int window, float scale) {
     int t = blockIdx.x, h = blockIdx.y;
     int b = seq_of[t];
-    size_t orow = size_t(t) * ldo + size_t(h) * hd;
+    size_t orow = size_t(t) * ldo + size_t(h) * hdv;
     if (b < 0) {
-        for (int d = threadIdx.x; d < hd; d += blockDim.x) gb_store(out, out_dtype, orow + d, 0.f);
+        for (int d = threadIdx.x; d < hdv; d += blockDim.x) gb_store(out, out_dtype, orow + d, 0.f);
         return;
     }
-    __shared__ float qs[AG_MAX_HD];
-    __shared__ float acc_s[AG_WARPS][AG_MAX_HD];
+    __shared__ float qs[MAX_HD];
+    __shared__ float acc_s[AG_WARPS][MAX_HD];
     __shared__ float m_s[AG_WARPS], l_s[AG_WARPS];
     for (int d = threadIdx.x; d < hd; d += blockDim.x) qs[d] = gb_load(q, q_dtype, size_t(t) * ldq + size_t(h) * hd + d);
     __syncthreads();
@@ -39,7 +42,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     int g = h / (nh / nkv);
     const int* trow = table + size_t(b) * table_width;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int C = AG_MAX_HD / 32;
+    constexpr int C = MAX_HD / 32;
     float acc[C];
 #pragma unroll
     for (int c = 0; c < C; ++c) acc[c] = 0.f;
@@ -51,8 +54,8 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
         float s = -INFINITY;
         long long off = 0;
         if (valid) {
-            off = (long long)gb_kv_offset(trow, ring_pages, j, g, nkv, hd);
-            const TC* kr = kc + off;
+            off = (long long)gb_kv_offset(trow, ring_pages, j, g, nkv, 1);        // the position's row number
+            const TC* kr = kc + off * hd;
             float dot = 0.f;
             for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], gb_to_float(kr[d]), dot);
             s = dot * scale;
@@ -67,11 +70,11 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
             float pv = __shfl_sync(0xffffffffu, pj, jj);
             long long o = __shfl_sync(0xffffffffu, off, jj);
             if (pv != 0.f) {
-                const TC* vr = vc + o;
+                const TC* vr = vc + o * v_row;
 #pragma unroll
                 for (int c = 0; c < C; ++c) {
                     int d = lane + 32 * c;
-                    if (d < hd) acc[c] = fmaf(pv, gb_to_float(vr[d]), acc[c]);
+                    if (d < hdv) acc[c] = fmaf(pv, gb_to_float(vr[d]), acc[c]);
                 }
             }
         }
@@ -80,7 +83,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
 #pragma unroll
     for (int c = 0; c < C; ++c) {
         int d = lane + 32 * c;
-        if (d < hd) acc_s[warp][d] = acc[c];
+        if (d < hdv) acc_s[warp][d] = acc[c];
     }
     if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
     __syncthreads();
@@ -91,35 +94,42 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
         wgt[w] = (m_s[w] == -INFINITY) ? 0.f : expf(m_s[w] - M);
         L += l_s[w] * wgt[w];
     }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < AG_WARPS; ++w) o += acc_s[w][d] * wgt[w];
         gb_store(out, out_dtype, orow + d, o / L);
     }
 }
 
-// q: [T, nh, hd] with rows ldq elements apart (already rotated); out: [T, nh*hd] with rows ldo
+// q: [T, nh, hd] with rows ldq elements apart (already rotated); out: [T, nh*hdv] with rows ldo
 // apart.  seq_of[t] is the token's row in the page table (or -1 for padding, which gives
-// zeros), pos[t] its position.  window 0 means all earlier keys.
+// zeros), pos[t] its position.  window 0 means all earlier keys.  Keys [pages, nkv, PAGE, hd]; values
+// [pages, nkv, PAGE, v_row] of which the first hdv entries count (hdv = v_row = hd for ordinary heads).
 GB_API int gb_attention_generic(const void* q, int q_dtype, long long ldq, void* out, int out_dtype, long long ldo,
-                                int T, int nh, int nkv, int hd, const int* seq_of, const int* pos, const int* table,
-                                int table_width, int ring_pages, const void* kcache, const void* vcache,
-                                int cache_dtype, int window, float scale, cudaStream_t stream) {
+                                int T, int nh, int nkv, int hd, int hdv, int v_row, const int* seq_of, const int* pos,
+                                const int* table, int table_width, int ring_pages, const void* kcache,
+                                const void* vcache, int cache_dtype, int window, float scale, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(q_dtype) && gb_is_dtype(out_dtype) && gb_is_dtype(cache_dtype), "gb_attention_generic: bad dtype");
     GB_REQUIRE(hd > 0 && hd <= AG_MAX_HD, "gb_attention_generic: head_dim %d is not in 1..%d", hd, AG_MAX_HD);
+    GB_REQUIRE(hdv > 0 && hdv <= AG_MAX_HD && v_row >= hdv, "gb_attention_generic: value size %d (rows of %d) is not in 1..%d", hdv, v_row, AG_MAX_HD);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_generic: %d heads are not a multiple of %d KV heads", nh, nkv);
     GB_REQUIRE(nh <= 65535, "gb_attention_generic: too many heads (%d)", nh);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0, "gb_attention_generic: bad cache geometry");
     if (T == 0) return 0;
     dim3 grid(T, nh);
-    if (cache_dtype == GB_F32)
-        attention_generic_kernel<float><<<grid, AG_WARPS * 32, 0, stream>>>(
-            q, q_dtype, ldq, out, out_dtype, ldo, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages,
-            (const float*)kcache, (const float*)vcache, window, scale);
-    else
-        attention_generic_kernel<__nv_bfloat16><<<grid, AG_WARPS * 32, 0, stream>>>(
-            q, q_dtype, ldq, out, out_dtype, ldo, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages,
-            (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, window, scale);
+#define AG_LAUNCH(TC, MAX_HD)                                                                                     \
+    attention_generic_kernel<TC, MAX_HD><<<grid, AG_WARPS * 32, 0, stream>>>(                                     \
+        q, q_dtype, ldq, out, out_dtype, ldo, nh, nkv, hd, hdv, v_row, seq_of, pos, table, table_width, ring_pages, \
+        (const TC*)kcache, (const TC*)vcache, window, scale)
+    const bool small = hd <= 256 && hdv <= 256;
+    if (cache_dtype == GB_F32) {
+        if (small) AG_LAUNCH(float, 256);
+        else AG_LAUNCH(float, AG_MAX_HD);
+    } else {
+        if (small) AG_LAUNCH(__nv_bfloat16, 256);
+        else AG_LAUNCH(__nv_bfloat16, AG_MAX_HD);
+    }
+#undef AG_LAUNCH
     GB_LAUNCH_OK("gb_attention_generic");
     return 0;
 }

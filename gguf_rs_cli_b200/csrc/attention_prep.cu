@@ -1,0 +1,206 @@
+// What stands between the projections of an attention mixer and the attention kernel when it is more than
+// a rotation: normalised queries and keys with a query temperature that grows with the position, and the
+// preparation of latent attention (the normalised latent row and the shared rotated key part go into the
+// cache; queries are brought into the latent's space by a product per head).  All in 32-bit.
+#include <math.h>
+
+#include "common.cuh"
+
+// ---------------------------------------- unit-RMS q and k, query temperature
+// One block per token; its warps take the token's heads in turn: q heads first (scaled in place), then k
+// heads (into the cache), then v heads (copied into the cache).
+//   q_h <- q_h / sqrt(mean(q_h^2) + eps) * temp(p),  temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1)
+//   k_g <- k_g / sqrt(mean(k_g^2) + eps)
+// normalise 0 leaves the division out; coef 0 the temperature.  Keys have D entries, values Dv.
+__global__ void qk_norm_kv_write_kernel(void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v,
+                                        int dtype, long long ld, int H, int G, int D, int Dv, int normalise, float eps,
+                                        float coef, int every, const int* __restrict__ seq_of,
+                                        const int* __restrict__ pos, const int* __restrict__ table, int table_width,
+                                        int ring_pages, void* __restrict__ kcache, void* __restrict__ vcache,
+                                        int cache_dtype) {
+    const int t = blockIdx.x;
+    const int b = seq_of[t];
+    if (b < 0) return;
+    const int p = pos[t];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const size_t row = size_t(t) * size_t(ld);
+    const int* trow = table + size_t(b) * table_width;
+    const float temp = coef != 0.f ? 1.f + coef * logf(float((p + 1) / every) + 1.f) : 1.f;
+    const int total = k ? H + 2 * G : H;
+    for (int item = warp; item < total; item += warps) {
+        if (item < H + G) {
+            const bool is_q = item < H;
+            const void* src = is_q ? q : k;
+            const size_t o = row + size_t(is_q ? item : item - H) * D;
+            float f = is_q ? temp : 1.f;
+            if (normalise) {
+                float ss = 0.f;
+                for (int d = lane; d < D; d += 32) {
+                    const float x = gb_load(src, dtype, o + d);
+                    ss = fmaf(x, x, ss);
+                }
+                f /= sqrtf(gb_warp_sum(ss) / float(D) + eps);
+            }
+            if (is_q) {
+                for (int d = lane; d < D; d += 32) gb_store(q, dtype, o + d, gb_load(q, dtype, o + d) * f);
+            } else {
+                const size_t c = gb_kv_offset(trow, ring_pages, p, item - H, G, D);
+                for (int d = lane; d < D; d += 32) gb_store(kcache, cache_dtype, c + d, gb_load(k, dtype, o + d) * f);
+            }
+        } else {
+            const int g = item - H - G;
+            const size_t o = row + size_t(g) * Dv;
+            const size_t c = gb_kv_offset(trow, ring_pages, p, g, G, Dv);
+            for (int d = lane; d < Dv; d += 32) gb_store(vcache, cache_dtype, c + d, gb_load(v, dtype, o + d));
+        }
+    }
+}
+
+// q [T, H*D] (scaled in place), k [T, G*D], v [T, G*Dv]: first elements of token 0's parts; rows `ld` apart.
+// kcache [pages, G, PAGE, D], vcache [pages, G, PAGE, Dv].  k and v null: only q is treated.
+GB_API int gb_qk_norm_kv_write(void* q, const void* k, const void* v, int dtype, long long ld, int T, int H, int G, int D,
+                               int Dv, int normalise, float eps, float coef, int every, const int* seq_of, const int* pos,
+                               const int* table, int table_width, int ring_pages, void* kcache, void* vcache,
+                               int cache_dtype, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(cache_dtype), "gb_qk_norm_kv_write: bad dtype");
+    GB_REQUIRE(H > 0 && G > 0 && D > 0 && Dv > 0, "gb_qk_norm_kv_write: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d", H, G, D, Dv);
+    GB_REQUIRE(!normalise || eps > 0.f, "gb_qk_norm_kv_write: eps must be positive");
+    GB_REQUIRE(coef == 0.f || every > 0, "gb_qk_norm_kv_write: the temperature's period must be positive, got %d", every);
+    GB_REQUIRE((k == nullptr) == (v == nullptr), "gb_qk_norm_kv_write: k and v must both be given or both be null");
+    GB_REQUIRE(!k || (table && kcache && vcache && ring_pages > 0 && table_width >= 1), "gb_qk_norm_kv_write: cache missing");
+    if (T == 0) return 0;
+    qk_norm_kv_write_kernel<<<T, 128, 0, stream>>>(q, k, v, dtype, ld, H, G, D, Dv, normalise, eps, coef, every > 0 ? every : 1,
+                                                   seq_of, pos, table, table_width, ring_pages, kcache, vcache, cache_dtype);
+    GB_LAUNCH_OK("gb_qk_norm_kv_write");
+    return 0;
+}
+
+// ------------------------------------------------------- latent attention
+// One block per token.  dkv [C + Rd]: the first C entries, divided by their root mean square and multiplied
+// by w, are the latent row c; the last Rd are a key part that all heads share, rotated by the token's
+// position.  Both go into the cache as one row [C + Rd].  q [H, D + Rd]: the last Rd entries of each head
+// are rotated likewise and written to qa [H, C + Rd] behind the C entries that the product per head fills.
+// Rotation: the first rot_dims entries of the part, pair (2i, 2i+1) by position * inv_freq[i]; the rest
+// pass unchanged.
+__global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, const void* __restrict__ dkv,
+                                   long long ldd, int dtype, int H, int D, int Rd, int C, int rot_dims,
+                                   const float* __restrict__ inv_freq, const void* __restrict__ w, int w_dtype, float eps,
+                                   void* __restrict__ qa, long long lda, const int* __restrict__ seq_of,
+                                   const int* __restrict__ pos, const int* __restrict__ table, int table_width,
+                                   int ring_pages, void* __restrict__ cache, int cache_dtype) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int b = seq_of[t];
+    if (b < 0) return;
+    const int p = pos[t];
+    const size_t drow = size_t(t) * size_t(ldd);
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < C; d += blockDim.x) {
+        const float x = gb_load(dkv, dtype, drow + d);
+        ss = fmaf(x, x, ss);
+    }
+    ss = gb_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int wv = 0; wv < (blockDim.x >> 5); ++wv) tot += red[wv];
+    const float f = 1.f / sqrtf(tot / float(C) + eps);
+    const size_t crow = gb_kv_offset(table + size_t(b) * table_width, ring_pages, p, 0, 1, C + Rd);
+    for (int d = threadIdx.x; d < C; d += blockDim.x)
+        gb_store(cache, cache_dtype, crow + d, gb_load(dkv, dtype, drow + d) * f * gb_load(w, w_dtype, d));
+    // rotated parts: item 0 is the shared key part, items 1..H the heads' query parts
+    const int half = rot_dims / 2, pairs = Rd / 2;          // Rd even: checked by the caller
+    for (int idx = threadIdx.x; idx < (H + 1) * pairs; idx += blockDim.x) {
+        const int item = idx / pairs, i = idx - item * pairs;
+        float sn = 0.f, cs = 1.f;
+        if (i < half) sincosf(float(p) * inv_freq[i], &sn, &cs);
+        float x0, x1, y0, y1;
+        if (item == 0) {
+            x0 = gb_load(dkv, dtype, drow + C + 2 * i);
+            x1 = gb_load(dkv, dtype, drow + C + 2 * i + 1);
+        } else {
+            const size_t o = size_t(t) * ldq + size_t(item - 1) * (D + Rd) + D + 2 * i;
+            x0 = gb_load(q, dtype, o);
+            x1 = gb_load(q, dtype, o + 1);
+        }
+        gb_rotate(x0, x1, cs, sn, y0, y1);
+        if (item == 0) {
+            gb_store(cache, cache_dtype, crow + C + 2 * i, y0);
+            gb_store(cache, cache_dtype, crow + C + 2 * i + 1, y1);
+        } else {
+            const size_t o = size_t(t) * lda + size_t(item - 1) * (C + Rd) + C + 2 * i;
+            gb_store(qa, dtype, o, y0);
+            gb_store(qa, dtype, o + 1, y1);
+        }
+    }
+}
+
+GB_API int gb_latent_prep(const void* q, long long ldq, const void* dkv, long long ldd, int dtype, int T, int H, int D, int Rd,
+                          int C, int rot_dims, const float* inv_freq, const void* w, int w_dtype, float eps, void* qa,
+                          long long lda, const int* seq_of, const int* pos, const int* table, int table_width,
+                          int ring_pages, void* cache, int cache_dtype, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(cache_dtype), "gb_latent_prep: bad dtype");
+    GB_REQUIRE(H > 0 && D >= 0 && C > 0 && Rd >= 0 && Rd % 2 == 0 && rot_dims >= 0 && rot_dims <= Rd && rot_dims % 2 == 0,
+               "gb_latent_prep: bad sizes heads=%d dim=%d rot_dim=%d kv_rank=%d rotated=%d", H, D, Rd, C, rot_dims);
+    GB_REQUIRE(rot_dims == 0 || inv_freq, "gb_latent_prep: no table of frequencies");
+    GB_REQUIRE(table && cache && ring_pages > 0 && table_width >= 1 && eps > 0.f, "gb_latent_prep: cache missing");
+    if (T == 0) return 0;
+    latent_prep_kernel<<<T, 128, 0, stream>>>(q, ldq, dkv, ldd, dtype, H, D, Rd, C, rot_dims, inv_freq, w, w_dtype, eps, qa, lda,
+                                              seq_of, pos, table, table_width, ring_pages, cache, cache_dtype);
+    GB_LAUNCH_OK("gb_latent_prep");
+    return 0;
+}
+
+// --------------------------------------------------- a product per head
+// out[t, h*os + o] = sum_i x[t, h*xs + i] * W[h, i, o] for o < O: every head has a matrix [I, O] of its own
+// (row-major, heads one after the other).  32-bit FMAs in ascending i, one thread per output column and
+// tile of HM_TOKENS tokens, so a token's result does not depend on the batch.
+constexpr int HM_TOKENS = 8;
+
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(128) head_matmul_kernel(const TX* __restrict__ x, long long ldx, int xs,
+                                                          const TW* __restrict__ W, int I, int O, void* __restrict__ out,
+                                                          int out_dtype, long long ldo, int os, int T) {
+    extern __shared__ float xt[];                     // [HM_TOKENS][I]
+    const int t0 = blockIdx.x * HM_TOKENS, h = blockIdx.y;
+    const int o = blockIdx.z * 128 + threadIdx.x;
+    const int nt = min(HM_TOKENS, T - t0);
+    for (int idx = threadIdx.x; idx < HM_TOKENS * I; idx += 128) {
+        const int tt = idx / I, i = idx - tt * I;
+        xt[idx] = tt < nt ? gb_to_float(x[size_t(t0 + tt) * ldx + size_t(h) * xs + i]) : 0.f;
+    }
+    __syncthreads();
+    if (o >= O) return;
+    float acc[HM_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = 0.f;
+    const TW* wp = W + size_t(h) * I * O + o;
+    for (int i = 0; i < I; ++i) {
+        const float wv = gb_to_float(wp[size_t(i) * O]);
+#pragma unroll
+        for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = fmaf(xt[tt * I + i], wv, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < HM_TOKENS; ++tt)
+        if (tt < nt) gb_store(out, out_dtype, size_t(t0 + tt) * ldo + size_t(h) * os + o, acc[tt]);
+}
+
+// x: head h's I inputs start at column h*xs of a row (rows ldx apart); out: its O results start at column h*os.
+GB_API int gb_head_matmul(const void* x, int x_dtype, long long ldx, int xs, const void* W, int w_dtype, int H, int I, int O,
+                          void* out, int out_dtype, long long ldo, int os, int T, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(x_dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(out_dtype), "gb_head_matmul: bad dtype");
+    GB_REQUIRE(H > 0 && H <= 65535 && I > 0 && O > 0 && xs >= I && os >= O, "gb_head_matmul: bad sizes heads=%d in=%d out=%d", H, I, O);
+    const size_t smem = size_t(HM_TOKENS) * I * sizeof(float);
+    GB_REQUIRE(smem <= 48 * 1024, "gb_head_matmul: %d inputs per head exceed %d", I, 48 * 1024 / (4 * HM_TOKENS));
+    if (T == 0) return 0;
+    dim3 grid((T + HM_TOKENS - 1) / HM_TOKENS, H, (O + 127) / 128);
+#define HM_LAUNCH(TX, TW)                                                                                             \
+    head_matmul_kernel<TX, TW><<<grid, 128, smem, stream>>>((const TX*)x, ldx, xs, (const TW*)W, I, O, out, out_dtype, ldo, os, T)
+    if (x_dtype == GB_F32 && w_dtype == GB_F32) HM_LAUNCH(float, float);
+    else if (x_dtype == GB_BF16 && w_dtype == GB_BF16) HM_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == GB_BF16 && w_dtype == GB_F32) HM_LAUNCH(__nv_bfloat16, float);
+    else HM_LAUNCH(float, __nv_bfloat16);
+#undef HM_LAUNCH
+    GB_LAUNCH_OK("gb_head_matmul");
+    return 0;
+}

@@ -96,6 +96,14 @@ __device__ __forceinline__ void gb_rotate(float x0, float x1, float cs, float sn
     y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
 }
 
+// Activation of the gate in a gated feed-forward: 1 SiLU z / (1 + exp(-z)); 2 GELU in its tanh form,
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  32-bit arithmetic.
+enum GbGateAct { GB_ACT_SILU = 1, GB_ACT_GELU_TANH = 2 };
+__device__ __forceinline__ float gb_gate_act(float z, int act) {
+    if (act == GB_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.f + expf(-z));
+}
+
 __device__ __forceinline__ float gb_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -7,7 +7,7 @@
 
 // ------------------------------------------------------------------ embedding
 __global__ void embed_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ tokens,
-                             int E, int V, float* __restrict__ out) {
+                             int E, int V, float scale, float* __restrict__ out) {
     gb_grid_launch_dependents();
     gb_grid_wait();
     int t = blockIdx.x;
@@ -18,23 +18,23 @@ __global__ void embed_kernel(const void* __restrict__ table, int table_dtype, co
         return;
     }
     size_t base = size_t(tok) * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = gb_load(table, table_dtype, base + i);
+    for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = gb_load(table, table_dtype, base + i) * scale;
 }
 
-// x[t,:] = table[tokens[t],:] as 32-bit floats (the residual stream is kept in 32-bit).
-GB_API int gb_embed(const void* table, int table_dtype, const int* tokens, int T, int E, int V, float* out,
+// x[t,:] = table[tokens[t],:] * scale as 32-bit floats (the residual stream is kept in 32-bit).
+GB_API int gb_embed(const void* table, int table_dtype, const int* tokens, int T, int E, int V, float scale, float* out,
                     cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(table_dtype), "gb_embed: bad table dtype %d", table_dtype);
     GB_REQUIRE(T >= 0 && E > 0 && V > 0, "gb_embed: bad sizes T=%d E=%d V=%d", T, E, V);
     if (T == 0) return 0;
-    gb_launch(embed_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, tokens, E, V, out);
+    gb_launch(embed_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, tokens, E, V, scale, out);
     GB_LAUNCH_OK("gb_embed");
     return 0;
 }
 
 // The same, and for the deferred norm of the first layer: xb[t,:] = bf16(x[t,:]) and ssq[t] = sum(x[t,:]^2).
 __global__ void embed_shadow_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ tokens,
-                                    int E, int V, float* __restrict__ out, __nv_bfloat16* __restrict__ xb,
+                                    int E, int V, float scale, float* __restrict__ out, __nv_bfloat16* __restrict__ xb,
                                     float* __restrict__ ssq) {
     __shared__ float red[32];
     gb_grid_launch_dependents();
@@ -45,7 +45,7 @@ __global__ void embed_shadow_kernel(const void* __restrict__ table, int table_dt
     size_t base = size_t(ok ? tok : 0) * E;
     float ss = 0.f;
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
-        float v = ok ? gb_load(table, table_dtype, base + i) : 0.f;
+        float v = ok ? gb_load(table, table_dtype, base + i) * scale : 0.f;
         out[size_t(t) * E + i] = v;
         xb[size_t(t) * E + i] = __float2bfloat16_rn(v);
         ss += v * v;
@@ -60,12 +60,12 @@ __global__ void embed_shadow_kernel(const void* __restrict__ table, int table_dt
     }
 }
 
-GB_API int gb_embed_shadow(const void* table, int table_dtype, const int* tokens, int T, int E, int V, float* out,
-                           void* xb, float* ssq, cudaStream_t stream) {
+GB_API int gb_embed_shadow(const void* table, int table_dtype, const int* tokens, int T, int E, int V, float scale,
+                           float* out, void* xb, float* ssq, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(table_dtype), "gb_embed_shadow: bad table dtype %d", table_dtype);
     GB_REQUIRE(T >= 0 && E > 0 && V > 0 && xb && ssq, "gb_embed_shadow: bad arguments");
     if (T == 0) return 0;
-    gb_launch(embed_shadow_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, tokens, E, V, out, (__nv_bfloat16*)xb, ssq);
+    gb_launch(embed_shadow_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, tokens, E, V, scale, out, (__nv_bfloat16*)xb, ssq);
     GB_LAUNCH_OK("gb_embed_shadow");
     return 0;
 }
@@ -359,24 +359,25 @@ GB_API int gb_rope_kv_write(void* q, const void* k, const void* v, int dtype, lo
 }
 
 // ------------------------------------------------------- gated activation
-// out[t,i] = silu(gu[t,i]) * gu[t,F+i], silu(z) = z / (1 + exp(-z)).
-__global__ void swiglu_kernel(const void* __restrict__ gu, long long ld, void* __restrict__ out, int T, int F, int dtype) {
+// out[t,i] = act(gu[t,i]) * gu[t,F+i], act one of GbGateAct (SiLU z / (1 + exp(-z)), or GELU's tanh form).
+__global__ void swiglu_kernel(const void* __restrict__ gu, long long ld, void* __restrict__ out, int T, int F, int dtype, int act) {
     size_t n = size_t(T) * F;
     for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < n; idx += size_t(gridDim.x) * blockDim.x) {
         size_t t = idx / F;
         int i = int(idx - t * F);
         float g = gb_load(gu, dtype, t * ld + i), u = gb_load(gu, dtype, t * ld + F + i);
-        gb_store(out, dtype, idx, g / (1.f + expf(-g)) * u);
+        gb_store(out, dtype, idx, gb_gate_act(g, act) * u);
     }
 }
 
-GB_API int gb_swiglu(const void* gu, long long ld, void* out, int T, int F, int dtype, cudaStream_t stream) {
+GB_API int gb_swiglu(const void* gu, long long ld, void* out, int T, int F, int dtype, int act, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype), "gb_swiglu: bad dtype");
+    GB_REQUIRE(act == GB_ACT_SILU || act == GB_ACT_GELU_TANH, "gb_swiglu: unknown gate activation %d", act);
     GB_REQUIRE(F > 0 && T >= 0 && ld >= 2LL * F, "gb_swiglu: bad sizes T=%d F=%d ld=%lld", T, F, ld);
     if (T == 0) return 0;
     size_t n = size_t(T) * F;
     int blocks = int((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    swiglu_kernel<<<blocks, 256, 0, stream>>>(gu, ld, out, T, F, dtype);
+    swiglu_kernel<<<blocks, 256, 0, stream>>>(gu, ld, out, T, F, dtype, act);
     GB_LAUNCH_OK("gb_swiglu");
     return 0;
 }

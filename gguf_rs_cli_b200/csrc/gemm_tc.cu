@@ -555,17 +555,18 @@ GB_API int gb_gemm_tc_supported(const void* X, long long ldx, const void* W, lon
 // (the kernel leaves them zero).  Both may be null: every CTA then takes whole tiles.
 // swiglu_features > 0: W is [2*64*ceil(F/64), K], row 2f being gate row f and row 2f+1 up row f (zero
 // rows pad the last tile), F = swiglu_features, and
-// out[t,f] = silu(gate_f) * up_f has F columns (src/model/llama.rs:399-401 in the product's epilogue).
+// out[t,f] = act(gate_f) * up_f has F columns (src/model/llama.rs:399-401 in the product's epilogue); act is
+// SiLU, or what gate_act names (GbGateAct) in gb_gemm_tc_fused.
 static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
                         void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
-                        int n_counters, int sms, int swiglu_features, const float* row_ssq, int ssq_parts, int norm_size,
+                        int n_counters, int sms, int swiglu_features, int gate_act, const float* row_ssq, int ssq_parts, int norm_size,
                         float eps, float* resid_x, void* resid_xb, float* ssq_out, long long ld_x, cudaStream_t stream);
 
 GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
                       void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
                       int n_counters, int sms, int swiglu_features, cudaStream_t stream) {
     return gemm_tc_impl(X, ldx, W, ldw, bias, bias_dtype, out, out_dtype, ldo, T, N, K, scratch, counters, n_counters, sms,
-                        swiglu_features, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, 0, stream);
+                        swiglu_features, GB_ACT_SILU, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, 0, stream);
 }
 
 // The same product with a deferred RMS norm on its input and/or a residual epilogue:
@@ -576,18 +577,19 @@ GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw
 //    tile of 128 features: the row_ssq of the product that reads xb next.
 GB_API int gb_gemm_tc_fused(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
                             void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
-                            int n_counters, int sms, int swiglu_features, const float* row_ssq, int ssq_parts,
+                            int n_counters, int sms, int swiglu_features, int gate_act, const float* row_ssq, int ssq_parts,
                             int norm_size, float eps, float* resid_x, void* resid_xb, float* ssq_out, long long ld_x,
                             cudaStream_t stream) {
     GB_REQUIRE(!row_ssq || (ssq_parts > 0 && norm_size > 0 && eps > 0.f), "gb_gemm_tc_fused: bad norm parameters");
     GB_REQUIRE(!resid_x || (resid_xb && ssq_out && ld_x >= N && !swiglu_features), "gb_gemm_tc_fused: bad residual parameters");
+    GB_REQUIRE(!swiglu_features || gate_act == GB_ACT_SILU || gate_act == GB_ACT_GELU_TANH, "gb_gemm_tc_fused: unknown gate activation %d", gate_act);
     return gemm_tc_impl(X, ldx, W, ldw, bias, bias_dtype, out, out_dtype, ldo, T, N, K, scratch, counters, n_counters, sms,
-                        swiglu_features, row_ssq, ssq_parts, norm_size, eps, resid_x, resid_xb, ssq_out, ld_x, stream);
+                        swiglu_features, gate_act, row_ssq, ssq_parts, norm_size, eps, resid_x, resid_xb, ssq_out, ld_x, stream);
 }
 
 static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
                         void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
-                        int n_counters, int sms, int swiglu_features, const float* row_ssq, int ssq_parts, int norm_size,
+                        int n_counters, int sms, int swiglu_features, int gate_act, const float* row_ssq, int ssq_parts, int norm_size,
                         float eps, float* resid_x, void* resid_xb, float* ssq_out, long long ld_x, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(out_dtype) && (!bias || gb_is_dtype(bias_dtype)), "gb_gemm_tc: bad dtype");
     GB_REQUIRE(T >= 0 && N > 0 && K > 0, "gb_gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
@@ -606,7 +608,7 @@ static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long l
     TcParams p;
     p.out = out; p.bias = bias; p.scratch = scratch; p.counters = counters; p.status = g_status_dev;
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
-    p.swiglu = swiglu_features > 0; p.N_out = swiglu_features; p.sms = sms;
+    p.swiglu = swiglu_features > 0 ? gate_act : 0; p.N_out = swiglu_features; p.sms = sms;
     cut.fill(p);
     p.row_ssq = row_ssq; p.ssq_parts = ssq_parts; p.norm_size = norm_size; p.eps = eps;
     p.resid_x = resid_x; p.resid_xb = (__nv_bfloat16*)resid_xb; p.ssq_out = ssq_out; p.ld_x = ld_x;

@@ -35,7 +35,7 @@ struct TcParams {
     long long ldo;
     int out_dtype, bias_dtype;
     int T, N, K;
-    int swiglu, N_out;    // swiglu: W's rows alternate gate, up; out has N_out features
+    int swiglu, N_out;    // swiglu (non-zero: the gate's activation, GbGateAct): W's rows alternate gate, up; out has N_out features
     int sms;
     // how the work is cut (see Unit): CTAs, tiles, and the rule that gives each CTA its share
     int n_ctas, tiles, cut;   // cut: CUT_WHOLE, CUT_EVEN or CUT_PER_TILE
@@ -261,7 +261,7 @@ __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t
                 const float gte = odd ? other[jj] : v[jj], up = odd ? v[8 + jj] : other[jj];
                 const int c = c0 + (odd ? 8 : 0) + jj;
                 if (mine(c))
-                    gb_store(p.out, p.out_dtype, size_t(t0 + c) * p.ldo + f, gte / (1.f + expf(-gte)) * up);
+                    gb_store(p.out, p.out_dtype, size_t(t0 + c) * p.ldo + f, gb_gate_act(gte, p.swiglu) * up);
             }
         }
     }

@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
 #pragma unroll
                         for (int jj = 0; jj < 8; ++jj) {
                             const float gte = odd ? other[jj] : v[jj], up = odd ? v[8 + jj] : other[jj];
-                            dst[((odd ? 8 : 0) + jj) * (BM / 2) + (row >> 1)] = __float2bfloat16_rn(gte / (1.f + expf(-gte)) * up);
+                            dst[((odd ? 8 : 0) + jj) * (BM / 2) + (row >> 1)] = __float2bfloat16_rn(gb_gate_act(gte, p.swiglu) * up);
                         }
                     }
                     fence_proxy_async();

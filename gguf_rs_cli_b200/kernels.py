@@ -17,17 +17,18 @@ def _cuda(*tensors) -> None:
             raise native.NativeError("kernels take CUDA tensors only; there is no CPU path")
 
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t,:] = table[tokens[t],:] in float32."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t,:] = table[tokens[t],:] * scale in float32."""
     _cuda(table, tokens, out)
     V, E = table.shape
     T = tokens.numel()
     assert out.dtype == torch.float32 and out.shape == (T, E) and out.is_contiguous() and tokens.dtype == torch.int32
-    call("gb_embed", ptr(table), dtype_code(table), ptr(tokens), T, E, V, ptr(out), stream_ptr())
+    call("gb_embed", ptr(table), dtype_code(table), ptr(tokens), T, E, V, float(scale), ptr(out), stream_ptr())
     return out
 
 
-def embed_shadow(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, xb: torch.Tensor, ssq: torch.Tensor) -> None:
+def embed_shadow(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, xb: torch.Tensor, ssq: torch.Tensor,
+                 scale: float = 1.0) -> None:
     """embed plus what a deferred norm needs: xb = bfloat16(out), ssq[t] = sum(out[t,:]^2)."""
     _cuda(table, tokens, out, xb, ssq)
     V, E = table.shape
@@ -35,7 +36,8 @@ def embed_shadow(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, x
     assert out.dtype == torch.float32 and out.shape == (T, E) and out.is_contiguous() and tokens.dtype == torch.int32
     assert xb.dtype == torch.bfloat16 and xb.shape == (T, E) and xb.is_contiguous() and ssq.dtype == torch.float32
     assert ssq.numel() >= T
-    call("gb_embed_shadow", ptr(table), dtype_code(table), ptr(tokens), T, E, V, ptr(out), ptr(xb), ptr(ssq), stream_ptr())
+    call("gb_embed_shadow", ptr(table), dtype_code(table), ptr(tokens), T, E, V, float(scale), ptr(out), ptr(xb), ptr(ssq),
+         stream_ptr())
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -75,22 +77,153 @@ def rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
-                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float) -> torch.Tensor:
+                      kcache: torch.Tensor, vcache: Optional[torch.Tensor], window: int, scale: float,
+                      v_dim: Optional[int] = None) -> torch.Tensor:
+    """v_dim: entries of a value when they differ from a key's head_dim.  vcache None: the values are the
+    first v_dim entries of the key rows themselves (one latent row per position serves as key and value)."""
     _cuda(q, out, seq_of, pos, table, kcache, vcache)
     T = q.shape[0]
-    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * head_dim)
+    v_dim = head_dim if v_dim is None else int(v_dim)
+    v_row = head_dim if vcache is None else vcache.shape[-1]
+    assert kcache.shape[-1] == head_dim and v_row >= v_dim and (vcache is None or vcache.dtype == kcache.dtype)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * v_dim)
     call("gb_attention_generic", ptr(q), dtype_code(q), q.stride(0), ptr(out), dtype_code(out), out.stride(0), T,
-         n_heads, n_kv_heads, head_dim, ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache),
-         ptr(vcache), dtype_code(kcache), int(window or 0), float(scale), stream_ptr())
+         n_heads, n_kv_heads, head_dim, v_dim, v_row, ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages,
+         ptr(kcache), ptr(kcache if vcache is None else vcache), dtype_code(kcache), int(window or 0), float(scale),
+         stream_ptr())
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """gate_up: [T, 2F], gate in the first F columns; out[t,i] = silu(gate)*up."""
+GATE_ACTS = {"silu": 1, "gelu_tanh": 2}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """gate_up: [T, 2F], gate in the first F columns; out[t,i] = act(gate)*up, act SiLU or GELU's tanh form."""
     _cuda(gate_up, out)
     T, F = out.shape
     assert gate_up.shape == (T, 2 * F) and gate_up.stride(1) == 1 and out.is_contiguous() and out.dtype == gate_up.dtype
-    call("gb_swiglu", ptr(gate_up), gate_up.stride(0), ptr(out), T, F, dtype_code(out), stream_ptr())
+    call("gb_swiglu", ptr(gate_up), gate_up.stride(0), ptr(out), T, F, dtype_code(out), GATE_ACTS[activation], stream_ptr())
+    return out
+
+
+def add_dyt(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor, alpha: float,
+            out: torch.Tensor, rows: Optional[torch.Tensor] = None, write_x: bool = True) -> torch.Tensor:
+    """Dynamic tanh with the residual add in front of it: v = x + delta (32-bit, written back to x),
+    out = tanh(alpha v) * weight + bias.  Arguments as add_rmsnorm."""
+    _cuda(x, delta, weight, bias, out, rows)
+    T, E = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    assert weight.numel() == E and bias.numel() == E and weight.dtype == bias.dtype
+    n_delta, stride = 0, 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == (T, E)
+        n_delta = 1 if delta.dim() == 2 else delta.shape[0]
+        stride = T * E
+    n_rows = T if rows is None else rows.numel()
+    assert out.shape == (n_rows, E)
+    call("gb_add_dyt", ptr(x), ptr(delta), 0 if delta is None else dtype_code(delta), n_delta, stride, ptr(rows), n_rows, E,
+         ptr(weight), ptr(bias), dtype_code(weight), float(alpha), ptr(out), dtype_code(out), int(write_x), stream_ptr())
+    return out
+
+
+def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x *= scale in place (float32, contiguous)."""
+    _cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    call("gb_scale", ptr(x), x.numel(), float(scale), stream_ptr())
+    return x
+
+
+def short_conv_silu(xin: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], ctx, out: torch.Tensor) -> torch.Tensor:
+    """out[t, c] = silu(sum_j taps[c, j] * xin[t - (K-1-j), c]) per sequence; rows before the step come from
+    state [slots, K-1, C] (float32), which is then renewed with the sequence's last K-1 inputs.
+    xin, out: [T, C] column slices (unit stride along c)."""
+    _cuda(xin, taps, state, out)
+    T, C = xin.shape
+    K = taps.shape[1]
+    assert taps.shape == (C, K) and taps.is_contiguous() and xin.stride(1) == 1 and out.stride(1) == 1
+    assert out.shape == (T, C) and out.dtype == xin.dtype
+    assert state is None or (state.dtype == torch.float32 and state.shape[1:] == (K - 1, C) and state.is_contiguous())
+    call("gb_short_conv_silu", ptr(xin), dtype_code(xin), xin.stride(0), T, ctx.B, C, K, ptr(taps), dtype_code(taps),
+         ptr(state), ptr(ctx.seq_of), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(out), out.stride(0), stream_ptr())
+    return out
+
+
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, a: torch.Tensor,
+               dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, out: torch.Tensor, ctx,
+               n_heads: int, n_kv_heads: int, dim: int, vdim: int, q_scale: float) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel over this step's tokens, from and into
+    state [slots, heads, dim, vdim] (float32).  q, k [T, kv_heads*dim] and v [T, heads*vdim] are column slices
+    of one buffer (after convolution and SiLU); beta [T, heads] and a [T, heads*dim] are the projections'
+    outputs before sigmoid and softplus; out float32 [T, heads*vdim] is what the state gives for q."""
+    _cuda(q, k, v, beta, a, dt_bias, a_log, state, out)
+    T = q.shape[0]
+    ld = q.stride(0)
+    assert k.stride(0) == ld and v.stride(0) == ld and q.dtype == k.dtype == v.dtype == beta.dtype == a.dtype
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and beta.stride(1) == 1 and a.stride(1) == 1
+    assert state.dtype == torch.float32 and state.shape[1:] == (n_heads, dim, vdim) and state.is_contiguous()
+    assert out.dtype == torch.float32 and out.shape == (T, n_heads * vdim) and out.stride(1) == 1
+    assert dt_bias.dtype == a_log.dtype and dt_bias.numel() == n_heads * dim and a_log.numel() == n_heads
+    call("gb_delta_rule", ptr(q), ptr(k), ptr(v), dtype_code(q), ld, ptr(beta), beta.stride(0), ptr(a), a.stride(0),
+         ptr(dt_bias), ptr(a_log), dtype_code(dt_bias), ptr(state), ptr(out), out.stride(0), ptr(ctx.cu), ptr(ctx.slots),
+         ptr(ctx.qlens), ctx.B, n_heads, n_kv_heads, dim, vdim, float(q_scale), stream_ptr())
+    return out
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                    n_heads: int, vdim: int) -> torch.Tensor:
+    """out[t,h,:] = o[t,h,:] / sqrt(mean(o[t,h,:]^2) + eps) * weight * sigmoid(gate[t,h,:]); o float32."""
+    _cuda(o, gate, weight, out)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
+    assert o.shape == gate.shape == out.shape == (T, n_heads * vdim) and weight.numel() == vdim
+    call("gb_gated_head_norm", ptr(o), o.stride(0), ptr(gate), dtype_code(gate), gate.stride(0), ptr(weight),
+         dtype_code(weight), float(eps), ptr(out), dtype_code(out), out.stride(0), T, n_heads, vdim, stream_ptr())
+    return out
+
+
+def qk_norm_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], n_heads: int, n_kv_heads: int,
+                     dim: int, vdim: int, normalise: bool, eps: float, temp_coef: float, temp_every: int,
+                     seq_of: torch.Tensor, pos: torch.Tensor, table: Optional[torch.Tensor], ring_pages: int,
+                     kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor]) -> None:
+    """q, k, v: column slices of one row-major buffer.  q heads are brought to unit root mean square and
+    multiplied by 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) in place; k heads normalised likewise
+    and v heads as they are go into the cache pages (keys of `dim`, values of `vdim` entries)."""
+    _cuda(q, k, v, seq_of, pos, table, kcache, vcache)
+    T, ld = q.shape[0], q.stride(0)
+    assert q.stride(1) == 1 and (k is None or (k.stride(0) == ld and v.stride(0) == ld and k.dtype == q.dtype == v.dtype))
+    assert kcache is None or (kcache.shape[-1] == dim and vcache.shape[-1] == vdim and kcache.dtype == vcache.dtype)
+    call("gb_qk_norm_kv_write", ptr(q), ptr(k), ptr(v), dtype_code(q), ld, T, n_heads, n_kv_heads, dim, vdim,
+         int(bool(normalise)), float(eps), float(temp_coef), int(temp_every), ptr(seq_of), ptr(pos), ptr(table),
+         0 if table is None else table.shape[1], ring_pages, ptr(kcache), ptr(vcache),
+         0 if kcache is None else dtype_code(kcache), stream_ptr())
+
+
+def latent_prep(q: torch.Tensor, dkv: torch.Tensor, n_heads: int, dim: int, rot_dim: int, kv_rank: int, rot_dims: int,
+                inv_freq: Optional[torch.Tensor], weight: torch.Tensor, eps: float, qa: torch.Tensor, seq_of: torch.Tensor,
+                pos: torch.Tensor, table: torch.Tensor, ring_pages: int, cache: torch.Tensor) -> None:
+    """Latent attention in front of the attention kernel: dkv [T, kv_rank + rot_dim] gives the cache row
+    (RMS-normed latent, rotated shared key part); the heads' rotated query parts go to qa [T, heads*(kv_rank +
+    rot_dim)] behind the kv_rank entries that head_matmul fills."""
+    _cuda(q, dkv, inv_freq, weight, qa, seq_of, pos, table, cache)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and dkv.stride(1) == 1 and qa.stride(1) == 1 and q.dtype == dkv.dtype == qa.dtype
+    assert q.shape[1] == n_heads * (dim + rot_dim) and dkv.shape[1] == kv_rank + rot_dim
+    assert qa.shape == (T, n_heads * (kv_rank + rot_dim)) and cache.shape[-1] == kv_rank + rot_dim and weight.numel() == kv_rank
+    call("gb_latent_prep", ptr(q), q.stride(0), ptr(dkv), dkv.stride(0), dtype_code(q), T, n_heads, dim, rot_dim, kv_rank,
+         rot_dims, ptr(inv_freq), ptr(weight), dtype_code(weight), float(eps), ptr(qa), qa.stride(0), ptr(seq_of), ptr(pos),
+         ptr(table), table.shape[1], ring_pages, ptr(cache), dtype_code(cache), stream_ptr())
+
+
+def head_matmul(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int) -> torch.Tensor:
+    """out[t, h*out_head_stride + o] = sum_i x[t, h*x_head_stride + i] * w[h, i, o]; w [heads, in, out]."""
+    _cuda(x, w, out)
+    H, I, O = w.shape
+    T = x.shape[0]
+    assert w.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T
+    assert x.shape[1] >= (H - 1) * x_head_stride + I and out.shape[1] >= (H - 1) * out_head_stride + O
+    call("gb_head_matmul", ptr(x), dtype_code(x), x.stride(0), int(x_head_stride), ptr(w), dtype_code(w), H, I, O, ptr(out),
+         dtype_code(out), out.stride(0), int(out_head_stride), T, stream_ptr())
     return out
 
 
@@ -181,10 +314,11 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor],
             split_k: bool = True, swiglu_features: int = 0, row_ssq: Optional[torch.Tensor] = None, ssq_parts: int = 0,
             norm_size: int = 0, eps: float = 0.0, resid_x: Optional[torch.Tensor] = None,
-            resid_xb: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+            resid_xb: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None,
+            gate_activation: str = "silu") -> Optional[torch.Tensor]:
     """bf16 x bf16 -> f32 accumulate on tcgen05; out bf16 or f32.  Refuses what
     gemm_tc_supported refuses.  With swiglu_features = F, w is interleave_gate_up(gate, up)
-    and out [T, F] = silu(x gate^T) * (x up^T).
+    and out [T, F] = act(x gate^T) * (x up^T), act = gate_activation (GATE_ACTS).
 
     row_ssq [ssq_parts, T]: x holds rows whose RMS norm is deferred (its weight folded into w); each
     token's results are scaled by 1 / sqrt(sum_i row_ssq[i, t] / norm_size + eps).
@@ -210,7 +344,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
             scratch, counters = sc.floats, sc.counters
     call("gb_gemm_tc_fused", ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias), 0 if bias is None else dtype_code(bias),
          ptr(out), 1 if out is None else dtype_code(out), 0 if out is None else out.stride(0), T, N, K, ptr(scratch),
-         ptr(counters), 0 if counters is None else counters.numel(), sc.sms, int(swiglu_features), ptr(row_ssq),
+         ptr(counters), 0 if counters is None else counters.numel(), sc.sms, int(swiglu_features),
+         GATE_ACTS[gate_activation], ptr(row_ssq),
          int(ssq_parts), int(norm_size), float(eps), ptr(resid_x), ptr(resid_xb), ptr(ssq_out),
          0 if resid_x is None else resid_x.stride(0), stream_ptr())
     return out

@@ -29,12 +29,14 @@ class Layer:
                 positions[key] = POSITIONS.get(spec.position.kind)(spec.position, dtype, device)
             position = positions[key]
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, dtype, device, position=position)
-        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
+        # a layer without a feed-forward is its mixer alone
+        self.feed_forward = None if spec.feed_forward is None else \
+            FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
         self.norms = {name: NORMS.get(s.kind)(s, dtype, device) for name, s in spec.norms.items()}
         self.block = BLOCKS.get(spec.block)(self.mixer, self.feed_forward, self.norms)
 
     def parts(self):
-        return [self.mixer, self.feed_forward] + list(self.norms.values())
+        return [p for p in (self.mixer, self.feed_forward) if p is not None] + list(self.norms.values())
 
 
 def _requests_of(spec: ModelSpec, parts) -> List[TensorRequest]:
@@ -79,7 +81,7 @@ class Decoder:
         computing = [self.embedding, self.final_norm, self.head]
         for r in spec.schedule:
             l = self.layers[r.layer]
-            computing += [l.block, l.mixer, l.feed_forward] + list(l.norms.values())
+            computing += [p for p in (l.block, l.mixer, l.feed_forward) if p is not None] + list(l.norms.values())
         for part in computing:
             key = plan_key_of(part)
             if hasattr(part, "plan") and key not in seen_plans:
@@ -151,7 +153,8 @@ class Decoder:
             if src in cache.group_of_run:
                 gi, i = cache.group_of_run[src]
                 g = cache.groups[gi]
-                views.append(RunView(r, run.layer, run.cache_of is None, gi, g.k[i], g.v[i], g.ring_pages, g.spec))
+                views.append(RunView(r, run.layer, run.cache_of is None, gi, g.k[i], None if g.v is None else g.v[i], g.ring_pages,
+                                      g.spec))
             else:
                 views.append(RunView(r, run.layer, False))
         return views

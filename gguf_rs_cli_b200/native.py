@@ -132,15 +132,23 @@ _SIGNATURES = {
     "gb_device_arch": [],
     "gb_sm_count": [],
     "gb_set_pdl": [_I],
-    "gb_embed": [_P, _I, _P, _I, _I, _I, _P, _P],
-    "gb_embed_shadow": [_P, _I, _P, _I, _I, _I, _P, _P, _P, _P],
-    "gb_gemm_tc_fused": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _L, _P],
+    "gb_embed": [_P, _I, _P, _I, _I, _I, _F, _P, _P],
+    "gb_embed_shadow": [_P, _I, _P, _I, _I, _I, _F, _P, _P, _P, _P],
+    "gb_gemm_tc_fused": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _L, _P],
     "gb_add_rmsnorm": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _I, _F, _P, _I, _I, _P],
     "gb_rope_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _P],
-    "gb_swiglu": [_P, _L, _P, _I, _I, _I, _P],
+    "gb_swiglu": [_P, _L, _P, _I, _I, _I, _I, _P],
     "gb_zero_rows": [_P, _P, _I, _I, _P],
     "gb_gemm_generic": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P],
-    "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _P],
+    "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _P],
+    "gb_add_dyt": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P],
+    "gb_scale": [_P, _L, _F, _P],
+    "gb_short_conv_silu": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _L, _P],
+    "gb_delta_rule": [_P, _P, _P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _P],
+    "gb_qk_norm_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P],
+    "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _P, _P, _P, _I, _I, _P, _I, _P],
+    "gb_head_matmul": [_P, _I, _L, _I, _P, _I, _I, _I, _I, _P, _I, _L, _I, _I, _P],
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
     "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "gb_gemm_tc_tile": [_I],
@@ -208,7 +216,7 @@ def library():
 
 _launches = 0
 # kernels launched by one call of an entry point, where that is not one
-KERNELS_PER_CALL = {}
+KERNELS_PER_CALL = {"gb_short_conv_silu": 2}
 
 
 def launch_count() -> int:

@@ -7,6 +7,12 @@ over the cached positions (src/model/llama.rs:374-394), output projection
 A window (not in the reference) limits each token to the last `window` positions and
 gives the layer a cache group of its own kind.  With `shares_kv`, the mixer has no k
 and v of its own and reads the cache of the run its schedule entry names.
+
+Three further options, none in the reference, for designs that bring positions in without a
+rotation: values of another size than keys (`v_head_dim`); queries and keys divided by their
+root mean square per head, without a weight (`qk_norm_eps`); and a query temperature that grows
+with the position, q <- q (1 + coef ln(floor((p + 1) / every) + 1)) (`q_temp`).  With any of them
+scores, softmax and the mix of values run in 32-bit in the general attention kernel.
 """
 from __future__ import annotations
 
@@ -25,8 +31,9 @@ from .registry import register_mixer
 @register_mixer("attention")
 class Attention(Part):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window (None or W),
-    bias (q/k/v biases), shares_kv (default False).
-    tensors: q [nh*hd, E], k, v [nkv*hd, E], o [E, nh*hd], optional q_bias, k_bias, v_bias."""
+    bias (q/k/v biases), shares_kv (default False), v_head_dim (default head_dim),
+    qk_norm_eps (default None: no normalisation), q_temp (default None, or {"coef", "every"}).
+    tensors: q [nh*hd, E], k [nkv*hd, E], v [nkv*vd, E], o [E, nh*vd], optional q_bias, k_bias, v_bias."""
 
     def __init__(self, spec, dtype, device, position=None):
         super().__init__(spec, dtype, device)
@@ -38,13 +45,23 @@ class Attention(Part):
         self.window = p.get("window") or None
         self.shares_kv = bool(p.get("shares_kv", False))
         self.position = position
+        self.vd = int(p.get("v_head_dim") or self.hd)
+        self.qk_norm_eps = p.get("qk_norm_eps")
+        temp = p.get("q_temp") or None
+        self.temp_coef, self.temp_every = (float(temp["coef"]), int(temp["every"])) if temp else (0.0, 1)
+        if temp and self.temp_every <= 0:
+            raise ValueError(f"attention: q_temp.every must be a positive whole number, got {temp['every']!r}")
+        # normalised q and k, a query temperature or values of their own size: the exact path
+        self.exact = self.vd != self.hd or self.qk_norm_eps is not None or self.temp_coef != 0.0
+        if self.exact and (position is not None or self.shares_kv):
+            raise ValueError("attention: qk_norm_eps, q_temp and v_head_dim go with neither a rotation nor shares_kv")
 
     def kv_spec(self) -> Optional[KVSpec]:
-        return None if self.shares_kv else KVSpec(self.nkv, self.hd, self.window)
+        return None if self.shares_kv else self.reads_kv_spec()
 
     def reads_kv_spec(self) -> KVSpec:
         """The kind of cache this mixer can read (its own, or another run's)."""
-        return KVSpec(self.nkv, self.hd, self.window)
+        return KVSpec(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd)
 
     def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         return {}
@@ -52,9 +69,9 @@ class Attention(Part):
     def tensor_requests(self) -> List[TensorRequest]:
         E, t = self.p["hidden_size"], self.spec.tensors
         names = ["q"] + ([] if self.shares_kv else ["k", "v"])
-        rows = {"q": self.nh * self.hd, "k": self.nkv * self.hd, "v": self.nkv * self.hd}
+        rows = {"q": self.nh * self.hd, "k": self.nkv * self.hd, "v": self.nkv * self.vd}
         req = [TensorRequest(t[n], (rows[n], E)) for n in names]
-        req.append(TensorRequest(t["o"], (E, self.nh * self.hd)))
+        req.append(TensorRequest(t["o"], (E, self.nh * self.vd)))
         if self.p.get("bias"):
             req += [TensorRequest(t[n + "_bias"], (rows[n],)) for n in names]
         return req
@@ -76,17 +93,19 @@ class Attention(Part):
 
     # ---- planning on the host
     def plan_key(self):
-        return ("attention", self.hd, self.window)
+        return ("attention", self.hd, self.window, self.exact)
 
     def plan(self, batch: HostBatch):
         """Prompts: the list of query tiles (sequence row, first query) that the prefill kernel's CTAs take."""
-        if batch.decode:
+        if batch.decode or self.exact:
             return {}
         return {"tiles": kernels.attention_prefill_tiles(batch.qlens)}
 
     def graph_class(self, batch: HostBatch):
         """The decode kernel splits each sequence's pages over CTAs by a rule of the longest sequence; steps
         of one class launch the same grid and may share a captured graph."""
+        if self.exact:
+            return ()                                  # one block per token and head, whatever the lengths
         return kernels.decode_split_class(min(batch.max_kv, self.window) if self.window else batch.max_kv)
 
     def absorb_input_norm(self, weight: torch.Tensor) -> bool:
@@ -101,6 +120,8 @@ class Attention(Part):
         nh, nkv, hd = self.nh, self.nkv, self.hd
         qkv = self.qkv(h, ctx)
         ctx.mark("qkv")
+        if self.exact:
+            return self._forward_exact(qkv, ctx, run, residual)
         q = qkv[:, :nh * hd]
         k = v = None
         if not self.shares_kv:
@@ -118,6 +139,22 @@ class Attention(Part):
         out = ctx.ws.get("attn.out", (h.shape[0], nh * hd), ctx.dtype)
         kernels.attention(q, out, nh, nkv, hd, ctx, table, run.ring_pages, run.k, run.v, self.window or 0, self.scale,
                           rope=rope, tiles=ctx.plan_of(self).get("tiles"))
+        ctx.mark("attention")
+        term = self.o(out, ctx, residual=residual)
+        ctx.mark("o")
+        return term
+
+    def _forward_exact(self, qkv, ctx: StepContext, run: RunView, residual) -> Optional[torch.Tensor]:
+        """q and k to unit root mean square, the query temperature and the cache write in one kernel, then
+        attention with 32-bit scores and weights over keys of hd and values of vd entries."""
+        nh, nkv, hd, vd = self.nh, self.nkv, self.hd, self.vd
+        q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+        table = ctx.tables[run.group]
+        kernels.qk_norm_kv_write(q, k, v, nh, nkv, hd, vd, self.qk_norm_eps is not None, self.qk_norm_eps or 1.0,
+                                 self.temp_coef, self.temp_every, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v)
+        out = ctx.ws.get("attn.out", (qkv.shape[0], nh * vd), ctx.dtype)
+        kernels.attention_generic(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
+                                  self.window or 0, self.scale, v_dim=vd)
         ctx.mark("attention")
         term = self.o(out, ctx, residual=residual)
         ctx.mark("o")

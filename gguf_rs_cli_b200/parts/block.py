@@ -22,6 +22,8 @@ class PreNormBlock:
         """After the weights are loaded: a part that can take the weight of the norm in front of it into
         its own matrix does so (then that norm costs no kernel when the stream carries a shadow)."""
         for name, part in (("mixer", self.mixer), ("feed_forward", self.feed_forward)):
+            if part is None:
+                continue
             give = getattr(self.norms[name], "fold_weight", None)
             take = getattr(part, "absorb_input_norm", None)
             if give and take and not self.absorbed[name]:
@@ -35,6 +37,8 @@ class PreNormBlock:
         else:
             term = self.mixer.forward(h, ctx, run)
         self._add(stream, term)
+        if self.feed_forward is None:
+            return
         h = self._norm("feed_forward", stream, ctx)
         ctx.mark("ff_norm")
         if getattr(self.feed_forward, "accepts_residual", False):

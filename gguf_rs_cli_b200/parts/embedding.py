@@ -16,7 +16,8 @@ from .registry import register_embedding, register_head
 
 @register_embedding("embedding")
 class Embedding(Part):
-    """params: vocab_size, hidden_size.  tensors: weight [V, E]."""
+    """params: vocab_size, hidden_size, scale (default 1: the rows are multiplied by it in 32-bit).
+    tensors: weight [V, E]."""
 
     def tensor_requests(self) -> List[TensorRequest]:
         return [TensorRequest(self.spec.tensors["weight"], (self.p["vocab_size"], self.p["hidden_size"]))]
@@ -28,7 +29,7 @@ class Embedding(Part):
 
     def forward(self, tokens: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         x = ctx.ws.get("x", (tokens.numel(), self.p["hidden_size"]), torch.float32)
-        return kernels.embed(self.weight, tokens, x)
+        return kernels.embed(self.weight, tokens, x, float(self.p.get("scale", 1.0)))
 
     def forward_stream(self, tokens: torch.Tensor, ctx: StepContext) -> Stream:
         """The residual stream of a step; in bfloat16 mode with the shadow (bfloat16 copy and sums of
@@ -40,7 +41,7 @@ class Embedding(Part):
         stream.xb = ctx.ws.get("stream.xb", (T, E), torch.bfloat16)
         stream.ssq = ctx.ws.get("stream.ssq", ((E + 127) // 128, T), torch.float32)
         stream.ssq_parts = 1
-        kernels.embed_shadow(self.weight, tokens, stream.x, stream.xb, stream.ssq)
+        kernels.embed_shadow(self.weight, tokens, stream.x, stream.xb, stream.ssq, float(self.p.get("scale", 1.0)))
         return stream
 
 
@@ -48,7 +49,7 @@ class Embedding(Part):
 class LMHead(Part):
     """params: vocab_size, hidden_size, tied_to (the tensor that stands in when the folder has no
     head matrix of its own, or None), tied (the configuration says the head is the embedding: the
-    random-weights mode then writes no matrix for it).
+    random-weights mode then writes no matrix for it), logit_scale (default 1: the logits are multiplied by it).
     tensors: weight [V, E].  As in the reference, presence decides: a folder that has the matrix
     uses it, one that lacks it uses `tied_to` (src/model/llama.rs:124)."""
 
@@ -65,4 +66,6 @@ class LMHead(Part):
         self.proj = Linear(store.get(self.tensor_requests()[0]), name="logits")
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return self.proj(h, ctx, out_dtype=torch.float32)
+        logits = self.proj(h, ctx, out_dtype=torch.float32)
+        scale = float(self.p.get("logit_scale", 1.0))
+        return logits if scale == 1.0 else kernels.scale_(logits, scale)

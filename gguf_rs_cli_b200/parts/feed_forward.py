@@ -1,6 +1,6 @@
 """Dense gated feed-forward: down(act(gate(h)) * up(h)) with act = SiLU
-(src/model/llama.rs:399-402, src/math/ops.rs:11).  gate and up are one matrix
-[2F, E] after loading, so one product reads h once."""
+(src/model/llama.rs:399-402, src/math/ops.rs:11), or GELU in its tanh form for designs that
+ask for it.  gate and up are one matrix [2F, E] after loading, so one product reads h once."""
 from __future__ import annotations
 
 from typing import List
@@ -18,13 +18,14 @@ from .registry import register_feed_forward
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(Part):
-    """params: hidden_size, intermediate_size, activation ("silu").
+    """params: hidden_size, intermediate_size, activation ("silu" or "gelu_tanh").
     tensors: gate [F, E], up [F, E], down [E, F]."""
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
-        if self.p.get("activation", "silu") != "silu":
-            raise ValueError(f"gated_mlp: activation {self.p['activation']!r} is not supported (silu)")
+        self.activation = self.p.get("activation", "silu")
+        if self.activation not in kernels.GATE_ACTS:
+            raise ValueError(f"gated_mlp: activation {self.activation!r} is not supported {sorted(kernels.GATE_ACTS)}")
 
     def tensor_requests(self) -> List[TensorRequest]:
         E, F, t = self.p["hidden_size"], self.p["intermediate_size"], self.spec.tensors
@@ -60,11 +61,11 @@ class GatedMLP(Part):
         norm = dict(row_ssq=h.ssq, ssq_parts=h.parts, norm_size=h.size, eps=h.eps) if isinstance(h, DeferredNorm) else {}
         rows = h.xb if norm else h
         if self.fused and kernels.gemm_tc_supported(rows, self.gate_up_tiles):
-            kernels.gemm_tc(rows, self.gate_up_tiles, None, act, swiglu_features=F, **norm)
+            kernels.gemm_tc(rows, self.gate_up_tiles, None, act, swiglu_features=F, gate_activation=self.activation, **norm)
         elif self.fused:
             raise RuntimeError("gated_mlp: the activations given do not fit the fused product it was loaded for")
         else:
-            kernels.swiglu(self.gate_up(h, ctx), act)
+            kernels.swiglu(self.gate_up(h, ctx), act, self.activation)
         ctx.mark("gate_up")
         term = self.down(act, ctx, residual=residual)
         ctx.mark("down")

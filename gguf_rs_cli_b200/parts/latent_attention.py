@@ -1,0 +1,97 @@
+"""Latent attention as the mixer of a layer: keys and values of all heads are products of one latent row
+per position, c = rms_norm(W_dkv h)[:kv_rank] * w, plus one rotated key part of rot_dim entries that all
+heads share; only these kv_rank + rot_dim numbers per position are cached.
+
+Per head the score is (q_plain . W_uk c + q_rot . k_rot) * scale and the value W_uv c.  The products
+with W_uk and W_uv are moved to the query's side: q' = W_uk^T q_plain lives in the latent's space, so a
+head's score is [q', q_rot] . [c, k_rot], the mix of values is the mix of latent rows, and W_uv is applied
+to that mix once per token.  The attention kernel then sees one key/value head of kv_rank + rot_dim entries
+whose first kv_rank entries are also its values.  Scores, softmax and mix run in 32-bit.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .. import kernels
+from ..cache.cache import KVSpec
+from ..weights.loader import TensorRequest, WeightStore
+from .base import Part, RunView, StepContext
+from .linear import Linear
+from .registry import register_mixer
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Part):
+    """params: hidden_size, heads, dim (unrotated q/k entries per head), rot_dim (rotated ones, behind them), vdim,
+    kv_rank, scale, eps (of the latent's norm).  position: a rotary table over the rot_dim part (its first
+    rotary_dim entries are rotated, in the table's pairing, which must be the interleaved one).
+    tensors: q [heads*(dim+rot_dim), E], dkv [kv_rank+rot_dim, E], dkv_norm [kv_rank], uk [heads*dim, kv_rank],
+    uv [heads*vdim, kv_rank], o [E, heads*vdim]."""
+
+    def __init__(self, spec, dtype, device, position=None):
+        super().__init__(spec, dtype, device)
+        p = self.p
+        self.H, self.D, self.R, self.Dv, self.C = p["heads"], p["dim"], p["rot_dim"], p["vdim"], p["kv_rank"]
+        self.position = position
+        if self.R % 2:
+            raise ValueError(f"latent_attention: rot_dim {self.R} must be even")
+        if position is not None and (position.pairing != 1 or position.rotary_dim > self.R):
+            raise ValueError("latent_attention: the rotation must pair neighbours and fit into rot_dim")
+
+    def kv_spec(self) -> Optional[KVSpec]:
+        return KVSpec(1, self.C + self.R, None, 0)
+
+    def reads_kv_spec(self) -> KVSpec:
+        return self.kv_spec()
+
+    def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        return {}
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        E, t = self.p["hidden_size"], self.spec.tensors
+        H, D, R, Dv, C = self.H, self.D, self.R, self.Dv, self.C
+        return [TensorRequest(t["q"], (H * (D + R), E)), TensorRequest(t["dkv"], (C + R, E)),
+                TensorRequest(t["dkv_norm"], (C,), init="ones"), TensorRequest(t["uk"], (H * D, C)),
+                TensorRequest(t["uv"], (H * Dv, C)), TensorRequest(t["o"], (E, H * Dv))]
+
+    def load(self, store: WeightStore) -> None:
+        q, dkv, norm, uk, uv, o = (store.get(r) for r in self.tensor_requests())
+        H, D, R, Dv, C = self.H, self.D, self.R, self.Dv, self.C
+        rows = H * (D + R)
+        self.off_dkv = (rows + 7) // 8 * 8
+        parts = [q]
+        if self.off_dkv > rows:
+            parts.append(torch.zeros(self.off_dkv - rows, q.shape[1], dtype=q.dtype, device=q.device))
+        parts.append(dkv.to(q.dtype))
+        self.proj = Linear(torch.cat(parts, dim=0).contiguous(), name="latent.proj")
+        self.norm_weight = norm
+        self.uk = uk.reshape(H, D, C).contiguous()                           # q' = q_plain W_uk[h]: [in D, out C]
+        self.uv_t = uv.reshape(H, Dv, C).transpose(1, 2).contiguous()        # value = mix W_uv[h]^T: [in C, out Dv]
+        self.o = Linear(o, name="latent.o")
+
+    accepts_residual = True
+    graph_class = ()              # one block per token and head, whatever the lengths
+
+    def forward(self, h, ctx: StepContext, run: RunView, residual=None) -> Optional[torch.Tensor]:
+        H, D, R, Dv, C = self.H, self.D, self.R, self.Dv, self.C
+        T = h.shape[0]
+        proj = self.proj(h, ctx)
+        ctx.mark("projections")
+        q, dkv = proj[:, :H * (D + R)], proj[:, self.off_dkv:self.off_dkv + C + R]
+        table = ctx.tables[run.group]
+        pos = self.position
+        qa = ctx.ws.get("latent.qa", (T, H * (C + R)), ctx.dtype)
+        kernels.latent_prep(q, dkv, H, D, R, C, 0 if pos is None else pos.rotary_dim, None if pos is None else pos.inv_freq,
+                            self.norm_weight, self.p["eps"], qa, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k)
+        kernels.head_matmul(q, D + R, self.uk, qa, C + R)
+        mix = ctx.ws.get("latent.mix", (T, H * C), ctx.dtype)
+        kernels.attention_generic(qa, mix, H, 1, C + R, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, None, 0,
+                                  float(self.p["scale"]), v_dim=C)
+        ctx.mark("attention")
+        values = ctx.ws.get("latent.values", (T, H * Dv), ctx.dtype)
+        kernels.head_matmul(mix, C, self.uv_t, values, Dv)
+        term = self.o(values, ctx, residual=residual)
+        ctx.mark("o")
+        return term

@@ -51,3 +51,34 @@ class RMSNorm(Part):
                 stream.drop_shadow()              # x has changed
             stream.pending = None
         return out
+
+
+@register_norm("dyt")
+class DynamicTanh(Part):
+    """Dynamic tanh in a norm's place: tanh(alpha x) * weight + bias, no mean and no variance.
+    params: size.  tensors: weight [size], bias [size], alpha [] (one scalar)."""
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        t, n = self.spec.tensors, self.p["size"]
+        return [TensorRequest(t["weight"], (n,), init="ones"), TensorRequest(t["bias"], (n,), init="zeros"),
+                TensorRequest(t["alpha"], (), init="const:0.5")]
+
+    def load(self, store: WeightStore) -> None:
+        w, b, a = (store.get(r) for r in self.tensor_requests())
+        self.weight, self.bias = w, b.to(w.dtype)
+        self.alpha = float(a.float().item()) if a.device.type != "meta" else 0.0
+
+    graph_class = ()
+
+    def apply(self, stream: Stream, ctx: StepContext, rows: Optional[torch.Tensor] = None, buffer: str = "normed",
+              absorbed: bool = False):
+        """Adds the stream's pending term into x (32-bit) and returns tanh(alpha x) * weight + bias of all rows,
+        or of `rows` only (x is then left as it is)."""
+        n = stream.x.shape[0] if rows is None else rows.numel()
+        out = ctx.ws.get(buffer, (n, self.p["size"]), ctx.dtype)
+        kernels.add_dyt(stream.x, stream.pending, self.weight, self.bias, self.alpha, out, rows=rows, write_x=rows is None)
+        if rows is None:
+            if stream.pending is not None:
+                stream.drop_shadow()
+            stream.pending = None
+        return out

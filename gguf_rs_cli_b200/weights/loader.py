@@ -42,9 +42,17 @@ class TensorRequest:
     shape: Tuple[int, ...]
     optional: bool = False
     fallback: Optional[str] = None      # another tensor's name that is used when this one is absent
-    # what the random-weights mode writes for it: "normal" (N(0, 0.02)), "ones", "zeros", or None (nothing:
+    # what the random-weights mode writes for it: "normal" (N(0, 0.02)), "ones", "zeros", "const:<value>",
+    # "uniform:<low>:<high>", or None (nothing:
     # the tensor is left out of the folder and its fallback stands in)
     init: Optional[str] = "normal"
+    # a size of -1 in `shape` is taken from the file (a rank that no configuration key names); the
+    # random-weights mode, which has no file, writes `init_shape` instead
+    init_shape: Optional[Tuple[int, ...]] = None
+
+
+def shape_matches(asked: Tuple[int, ...], found: Tuple[int, ...]) -> bool:
+    return len(asked) == len(found) and all(a == -1 or a == f for a, f in zip(asked, found))
 
 
 class TensorSource:
@@ -131,7 +139,7 @@ class WeightStore:
                     continue
             asked.add(name)
             found = self.source.shape(name)
-            if tuple(found) != tuple(r.shape):
+            if not shape_matches(tuple(r.shape), tuple(found)):
                 wrong.append((name, tuple(r.shape), tuple(found)))
         unexpected = sorted(n for n in self.source.names()
                             if n not in asked and not any(fnmatch.fnmatchcase(n, pat) for pat in patterns))

@@ -35,8 +35,15 @@ def random_tensor(name: str, shape: Tuple[int, ...], seed: int, dtype=torch.bflo
         return torch.ones(shape, dtype=dtype, device=device)
     if init == "zeros":
         return torch.zeros(shape, dtype=dtype, device=device)
+    if init.startswith("const:"):
+        return torch.full(shape, float(init[6:]), dtype=dtype, device=device)
+    if init.startswith("uniform:"):                      # uniform:lo:hi
+        lo, hi = (float(x) for x in init[8:].split(":"))
+        g = torch.Generator(device=device).manual_seed(_seed_of(seed, name))
+        return (torch.rand(shape, generator=g, dtype=torch.float32, device=device) * (hi - lo) + lo).to(dtype)
     if init != "normal":
-        raise ValueError(f"{name}: the random-weights mode knows no initial value {init!r} (normal, ones, zeros)")
+        raise ValueError(f"{name}: the random-weights mode knows no initial value {init!r} "
+                         f"(normal, ones, zeros, const:<value>, uniform:<low>:<high>)")
     g = torch.Generator(device=device).manual_seed(_seed_of(seed, name))
     return (torch.randn(shape, generator=g, dtype=torch.float32, device=device) * STD).to(dtype)
 
@@ -56,7 +63,10 @@ def random_tensors(raw_config: Dict, seed: int, dtype=torch.bfloat16, device="cp
         if r.init is None:
             continue
         if r.name not in out:
-            out[r.name] = random_tensor(r.name, r.shape, seed, dtype, device, init=r.init)
+            shape = r.init_shape if r.init_shape is not None else r.shape
+            if any(n < 0 for n in shape):
+                raise ValueError(f"{r.name}: a size is left to the file ({list(r.shape)}) and no shape is given for random weights")
+            out[r.name] = random_tensor(r.name, shape, seed, dtype, device, init=r.init)
     return out
 
 
