@@ -4,6 +4,7 @@ one B200.  Prints one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--layers L] [--batch B] [--no-points] [--prompt-steps 128,256] [--shape 8b|1b|13b]
+                    [--design debonex [--sizes 1b,8b]]
 
 `value` is decoded tokens a second at batch 8 after 512-token prompts, timed on the
 device with CUDA events around K decode steps (each step: index arrays host to
@@ -274,6 +275,114 @@ def run_workload(name, layers_arg, pk):
     return 0
 
 
+# ---------------------------------------------------------------- another design beside Llama at equal size
+# Layer sizes that resemble a real model's, for `--design debonex`: the design's three mixers in turn
+# (delta rule, latent attention, delta rule, attention) beside a Llama of the same width, heads, feed-forward,
+# vocabulary and number of layers.
+DESIGN_SIZES = {
+    "1b": dict(width=2048, ff=8192, heads=16, kv_heads=4, head=128, kv_rank=512, rot=64, latent_dim=64, layers=8, vocab=32000),
+    "8b": dict(width=4096, ff=14336, heads=32, kv_heads=8, head=128, kv_rank=512, rot=64, latent_dim=64, layers=4, vocab=32000),
+    # latent attention with 128 unrotated and 64 rotated entries per head: no tiled kernel takes keys of 192
+    "1b-wide-latent": dict(width=2048, ff=8192, heads=16, kv_heads=4, head=128, kv_rank=512, rot=64, latent_dim=128, layers=4,
+                           vocab=32000),
+}
+
+
+def debonex_config(z):
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    delta = {"type": "channel_delta", "mlp": mlp,
+             "mixer": {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["head"], "vdim": z["head"], "conv": 4}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": z["heads"], "dim": z["latent_dim"], "rot_dim": z["rot"], "rot": {"base": 10000.0, "dims": z["rot"]},
+                        "kv_rank": z["kv_rank"], "vdim": z["head"], "scale": (z["latent_dim"] + z["rot"]) ** -0.5}}
+    attn = {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"],
+                      "scale": z["head"] ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}}
+    pattern = [delta, latent, delta, attn]
+    return {"architecture": "Debonex", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+            "norm": {"eps": 1e-5}, "layers": [pattern[i % 4] for i in range(z["layers"])]}
+
+
+def llama_config(z):
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": z["layers"],
+            "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"],
+            "head_dim": z["head"], "intermediate_size": z["ff"], "vocab_size": z["vocab"], "rope_theta": 10000.0,
+            "rope_scaling": None, "rms_norm_eps": 1e-5, "max_position_embeddings": CONTEXT, "tie_word_embeddings": False,
+            "hidden_act": "silu"}
+
+
+def stage_times(llm, lens, starts=0, reps=3):
+    """Milliseconds per stage of one eager step (sequences of `lens` new tokens each after `starts` cached
+    positions), summed over the layers of each kind of mixer and divided by their number: {kind.stage: ms}."""
+    import torch
+    from gguf_rs_cli_b200.engine.step import Entry
+    from gguf_rs_cli_b200.parts.base import Stream
+    eng = llm.engine(n_tokens=64 * CONTEXT, n_slots=64, max_len=CONTEXT)
+    model, best = llm.model, {}
+    for rep in range(reps + 1):
+        slots = [eng.open() for _ in lens]
+        if starts:
+            eng.step([Entry(s, [1] * starts, ()) for s in slots])
+        ctx, _, _ = eng.plan([Entry(s, [1] * n, ()) for s, n in zip(slots, lens)])
+        ctx.marks, ctx.mark_detail = [], True
+        stream = Stream(model.embedding.forward(ctx.tokens, ctx))
+        kinds = []
+        for view in eng.runs:
+            kind = model.spec.layers[view.layer].mixer.kind
+            ctx.mark(f"{kind}.begin")
+            n0 = len(ctx.marks)
+            model.layers[view.layer].block.forward(stream, ctx, view)
+            ctx.marks[n0:] = [(f"{kind}.{label}", ev) for label, ev in ctx.marks[n0:]]
+            kinds.append(kind)
+        torch.cuda.synchronize()
+        eng.check()
+        for s in slots:
+            eng.close(s)
+        if rep == 0:
+            continue
+        total = {}
+        for (_, a), (label, b) in zip(ctx.marks, ctx.marks[1:]):
+            if not label.endswith(".begin"):
+                total[label] = total.get(label, 0.0) + a.elapsed_time(b)
+        for label, ms in total.items():
+            ms /= kinds.count(label.split(".")[0])
+            best[label] = min(best.get(label, ms), ms)
+    return {k: round(v, 4) for k, v in best.items()}
+
+
+def run_design(args, pk):
+    """Prefill and decode throughput of another design at a few layer sizes, beside Llama at equal size.  One JSON line."""
+    import torch
+    from gguf_rs_cli_b200.api import from_random
+    warmup = max(args.warmup, 3)
+    out = {"metric": f"{args.design} beside llama at equal size: prefill tok/s ({PREFILL_TOKENS} tokens), decode tok/s @ batch "
+                     f"{args.batch} ({PROMPT}-token prompts)", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+           "dtype": "bf16", "data": "synthetic token ids, random weights", "impl": "ours", "peaks": pk, "sizes": {}}
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = sampler.mark()
+    for name in [x for x in args.sizes.split(",") if x.strip()]:
+        z = DESIGN_SIZES[name]
+        row = {"config": z}
+        for arm, raw in ((args.design, debonex_config(z)), ("llama", llama_config(z))):
+            llm = from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
+            torch.cuda.synchronize()
+            cfg = {"vocab_size": z["vocab"]}
+            tok_s, ms, launches, _ = measure_decode(llm, args.batch, args.steps, warmup, cfg)
+            pms = measure_prefill(llm, cfg, z["layers"])
+            row[arm] = {"decode_tok_s": round(tok_s, 1), "decode_ms_per_step": round(ms, 4), "decode_launches": launches,
+                        "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pms, 1), "prefill_ms": round(pms, 3),
+                        "prefill_stages_ms": stage_times(llm, [PREFILL_TOKENS]),
+                        "decode_stages_ms": stage_times(llm, [1] * args.batch, starts=PROMPT)}
+            del llm
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    out["clocks"] = sampler.summary(t0, sampler.mark())
+    sampler.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -290,6 +399,9 @@ def main():
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--rep-penalty", type=float, default=1.0)
     ap.add_argument("--prompt-steps", default="", help="also time prompt steps of these many tokens, e.g. 128,256,512")
+    ap.add_argument("--design", default=None, choices=["debonex"],
+                    help="instead of the headline line: prefill and decode of this design beside Llama at equal size")
+    ap.add_argument("--sizes", default="1b,8b", help=f"layer sizes of --design: {sorted(DESIGN_SIZES)}")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -300,6 +412,8 @@ def main():
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(args.warmup, 3)
+    if args.design:
+        return run_design(args, peaks())
     if args.shape != "8b":
         return run_workload(args.shape, args.layers, peaks())
     if args.layers is None:

@@ -9,6 +9,12 @@
 //
 // Sizes: head_dim 64 or 128 here (other sizes take the generic kernel), any group
 // size, any window, sequences that start anywhere in their cache.
+//
+// EXACT (for designs that ask for 32-bit attention weights): the weights p are not rounded to bfloat16.
+// Each p is split into three bfloat16 terms, p = hi + mid + lo (8 + 8 + 8 bits: all 24 of a float's
+// mantissa), and P V is three products with the same V fragments; every product p_x * v is then exact
+// and the sums are 32-bit, which is what 32-bit FMAs over float p and bfloat16 v would give up to the
+// order of the sums.  Scores are 32-bit sums of exact products of bfloat16 q and k either way.
 #include <math.h>
 
 #include "common.cuh"
@@ -67,8 +73,16 @@ template <int HD> __device__ __forceinline__ int swz(int row, int chunk) {
     return row * HD + (((chunk & ~7) | ((chunk ^ row) & 7)) << 3);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(AP_THREADS, 2) attention_prefill_kernel(ApParams p) {
+// p as three bfloat16 terms whose sum is p exactly (p >= 0 is a normal float or zero here)
+__device__ __forceinline__ void split3(float p, float& hi, float& mid, float& lo) {
+    hi = __bfloat162float(__float2bfloat16_rn(p));
+    const float r1 = p - hi;
+    mid = __bfloat162float(__float2bfloat16_rn(r1));
+    lo = r1 - mid;                               // at most 8 significant bits are left: exact as bfloat16
+}
+
+template <int HD, bool EXACT>
+__global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_kernel(ApParams p) {
     constexpr int CH = HD / 8;            // 16-byte chunks per row
     constexpr int KS = HD / 16;           // k-steps of Q.K^T
     constexpr int NT = AP_BN / 8;         // score n-tiles per warp (8 keys each)
@@ -187,8 +201,12 @@ __global__ void __launch_bounds__(AP_THREADS, 2) attention_prefill_kernel(ApPara
             float p2 = exp2f(s[j][2] * p.scale_log2 - ms1), p3 = exp2f(s[j][3] * p.scale_log2 - ms1);
             sum0 += p0 + p1;
             sum1 += p2 + p3;
-            pf[j][0] = pack_bf16(p0, p1);
-            pf[j][1] = pack_bf16(p2, p3);
+            if (EXACT) {
+                s[j][0] = p0; s[j][1] = p1; s[j][2] = p2; s[j][3] = p3;      // kept in 32-bit for the three-term split
+            } else {
+                pf[j][0] = pack_bf16(p0, p1);
+                pf[j][1] = pack_bf16(p2, p3);
+            }
         }
         l0 = l0 * a0 + sum0;
         l1 = l1 * a1 + sum1;
@@ -199,14 +217,36 @@ __global__ void __launch_bounds__(AP_THREADS, 2) attention_prefill_kernel(ApPara
         // ---- O += P V
 #pragma unroll
         for (int kk = 0; kk < AP_BN / 16; ++kk) {
+            unsigned ph[4], pm[4], pl[4];           // EXACT: the A fragment of these 16 keys as three terms
+            if (EXACT) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    float h4[4], m4[4], l4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) split3(s[2 * kk + half][e], h4[e], m4[e], l4[e]);
+                    ph[2 * half] = pack_bf16(h4[0], h4[1]); ph[2 * half + 1] = pack_bf16(h4[2], h4[3]);
+                    pm[2 * half] = pack_bf16(m4[0], m4[1]); pm[2 * half + 1] = pack_bf16(m4[2], m4[3]);
+                    pl[2 * half] = pack_bf16(l4[0], l4[1]); pl[2 * half + 1] = pack_bf16(l4[2], l4[3]);
+                }
+            }
 #pragma unroll
             for (int i2 = 0; i2 < OT / 2; ++i2) {
                 unsigned b0, b1, b2, b3;
                 // keys 16*kk .. +15, dims 16*i2 .. +15, transposed: lanes 0-7 / 8-15 / 16-23 / 24-31 address
                 // (keys 0-7, d lo), (keys 8-15, d lo), (keys 0-7, d hi), (keys 8-15, d hi)
                 ldmatrix_x4_trans(b0, b1, b2, b3, vt + swz<HD>(kk * 16 + (lane & 15), 2 * i2 + (lane >> 4)));
-                mma_bf16(o[2 * i2], pf[2 * kk][0], pf[2 * kk][1], pf[2 * kk + 1][0], pf[2 * kk + 1][1], b0, b1);
-                mma_bf16(o[2 * i2 + 1], pf[2 * kk][0], pf[2 * kk][1], pf[2 * kk + 1][0], pf[2 * kk + 1][1], b2, b3);
+                if (EXACT) {
+                    // smallest terms first
+                    mma_bf16(o[2 * i2], pl[0], pl[1], pl[2], pl[3], b0, b1);
+                    mma_bf16(o[2 * i2 + 1], pl[0], pl[1], pl[2], pl[3], b2, b3);
+                    mma_bf16(o[2 * i2], pm[0], pm[1], pm[2], pm[3], b0, b1);
+                    mma_bf16(o[2 * i2 + 1], pm[0], pm[1], pm[2], pm[3], b2, b3);
+                    mma_bf16(o[2 * i2], ph[0], ph[1], ph[2], ph[3], b0, b1);
+                    mma_bf16(o[2 * i2 + 1], ph[0], ph[1], ph[2], ph[3], b2, b3);
+                } else {
+                    mma_bf16(o[2 * i2], pf[2 * kk][0], pf[2 * kk][1], pf[2 * kk + 1][0], pf[2 * kk + 1][1], b0, b1);
+                    mma_bf16(o[2 * i2 + 1], pf[2 * kk][0], pf[2 * kk][1], pf[2 * kk + 1][0], pf[2 * kk + 1][1], b2, b3);
+                }
             }
         }
         __syncthreads();            // everyone is done with this buffer before it is loaded again
@@ -228,15 +268,15 @@ __global__ void __launch_bounds__(AP_THREADS, 2) attention_prefill_kernel(ApPara
     }
 }
 
-template <int HD> int launch_ap(const ApParams& p, int n_tiles, cudaStream_t stream) {
+template <int HD, bool EXACT> int launch_ap(const ApParams& p, int n_tiles, cudaStream_t stream) {
     constexpr int SMEM = (AP_BM + 4 * AP_BN) * HD * 2;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_prefill_kernel<HD, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return gb_fail("gb_attention_prefill: cannot get %d bytes of shared memory", SMEM);
         configured = true;
     }
-    gb_launch(attention_prefill_kernel<HD>, dim3(p.nh, n_tiles), dim3(AP_THREADS), SMEM, stream, p);
+    gb_launch(attention_prefill_kernel<HD, EXACT>, dim3(p.nh, n_tiles), dim3(AP_THREADS), SMEM, stream, p);
     GB_LAUNCH_OK("gb_attention_prefill");
     return 0;
 }
@@ -254,7 +294,7 @@ GB_API int gb_attention_prefill_tile() { return AP_BM; }
 GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long long ldo, int nh, int nkv, int hd,
                                 const int* tiles, int n_tiles, const int* cu, const int* starts, const int* qlens,
                                 const int* table, int table_width, int ring_pages, const void* kcache,
-                                const void* vcache, int window, float scale, cudaStream_t stream) {
+                                const void* vcache, int window, float scale, int exact, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_prefill_supported(hd, GB_BF16, GB_BF16), "gb_attention_prefill: head_dim %d is not 64 or 128", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_prefill: bad head counts %d / %d", nh, nkv);
     GB_REQUIRE(n_tiles <= 65535, "gb_attention_prefill: %d tiles of queries are too many for one launch", n_tiles);
@@ -268,5 +308,6 @@ GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long lo
     p.vc = (const __nv_bfloat16*)vcache; p.tiles = tiles; p.cu = cu; p.starts = starts; p.qlens = qlens; p.table = table;
     p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.table_width = table_width; p.ring_pages = ring_pages;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
-    return hd == 64 ? launch_ap<64>(p, n_tiles, stream) : launch_ap<128>(p, n_tiles, stream);
+    if (exact) return hd == 64 ? launch_ap<64, true>(p, n_tiles, stream) : launch_ap<128, true>(p, n_tiles, stream);
+    return hd == 64 ? launch_ap<64, false>(p, n_tiles, stream) : launch_ap<128, false>(p, n_tiles, stream);
 }

@@ -78,14 +78,17 @@ GB_API int gb_qk_norm_kv_write(void* q, const void* k, const void* v, int dtype,
 // ------------------------------------------------------- latent attention
 // One block per token.  dkv [C + Rd]: the first C entries, divided by their root mean square and multiplied
 // by w, are the latent row c; the last Rd are a key part that all heads share, rotated by the token's
-// position.  Both go into the cache as one row [C + Rd].  q [H, D + Rd]: the last Rd entries of each head
-// are rotated likewise and written to qa [H, C + Rd] behind the C entries that the product per head fills.
+// position.  Both go into the cache as one row [C + Rd] (and into row_out, a plain copy [T, C + Rd] of
+// this step's rows, when given).  q [H, D + Rd]: the last Rd entries of each head are rotated likewise and
+// written to qa, head h's part starting at entry h * qa_stride + qa_off of the token's row (qa may be q
+// itself: the rotation is then done in place).
 // Rotation: the first rot_dims entries of the part, pair (2i, 2i+1) by position * inv_freq[i]; the rest
 // pass unchanged.
 __global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, const void* __restrict__ dkv,
                                    long long ldd, int dtype, int H, int D, int Rd, int C, int rot_dims,
                                    const float* __restrict__ inv_freq, const void* __restrict__ w, int w_dtype, float eps,
-                                   void* __restrict__ qa, long long lda, const int* __restrict__ seq_of,
+                                   void* qa, long long lda, int qa_stride, int qa_off, void* __restrict__ row_out,
+                                   const int* __restrict__ seq_of,
                                    const int* __restrict__ pos, const int* __restrict__ table, int table_width,
                                    int ring_pages, void* __restrict__ cache, int cache_dtype) {
     __shared__ float red[32];
@@ -106,8 +109,12 @@ __global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, co
     for (int wv = 0; wv < (blockDim.x >> 5); ++wv) tot += red[wv];
     const float f = 1.f / sqrtf(tot / float(C) + eps);
     const size_t crow = gb_kv_offset(table + size_t(b) * table_width, ring_pages, p, 0, 1, C + Rd);
-    for (int d = threadIdx.x; d < C; d += blockDim.x)
-        gb_store(cache, cache_dtype, crow + d, gb_load(dkv, dtype, drow + d) * f * gb_load(w, w_dtype, d));
+    const size_t rrow = size_t(t) * (C + Rd);
+    for (int d = threadIdx.x; d < C; d += blockDim.x) {
+        const float cv = gb_load(dkv, dtype, drow + d) * f * gb_load(w, w_dtype, d);
+        gb_store(cache, cache_dtype, crow + d, cv);
+        if (row_out) gb_store(row_out, dtype, rrow + d, cv);
+    }
     // rotated parts: item 0 is the shared key part, items 1..H the heads' query parts
     const int half = rot_dims / 2, pairs = Rd / 2;          // Rd even: checked by the caller
     for (int idx = threadIdx.x; idx < (H + 1) * pairs; idx += blockDim.x) {
@@ -127,8 +134,12 @@ __global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, co
         if (item == 0) {
             gb_store(cache, cache_dtype, crow + C + 2 * i, y0);
             gb_store(cache, cache_dtype, crow + C + 2 * i + 1, y1);
+            if (row_out) {
+                gb_store(row_out, dtype, rrow + C + 2 * i, y0);
+                gb_store(row_out, dtype, rrow + C + 2 * i + 1, y1);
+            }
         } else {
-            const size_t o = size_t(t) * lda + size_t(item - 1) * (C + Rd) + C + 2 * i;
+            const size_t o = size_t(t) * lda + size_t(item - 1) * qa_stride + qa_off + 2 * i;
             gb_store(qa, dtype, o, y0);
             gb_store(qa, dtype, o + 1, y1);
         }
@@ -137,8 +148,9 @@ __global__ void latent_prep_kernel(const void* __restrict__ q, long long ldq, co
 
 GB_API int gb_latent_prep(const void* q, long long ldq, const void* dkv, long long ldd, int dtype, int T, int H, int D, int Rd,
                           int C, int rot_dims, const float* inv_freq, const void* w, int w_dtype, float eps, void* qa,
-                          long long lda, const int* seq_of, const int* pos, const int* table, int table_width,
-                          int ring_pages, void* cache, int cache_dtype, cudaStream_t stream) {
+                          long long lda, int qa_stride, int qa_off, void* row_out, const int* seq_of, const int* pos,
+                          const int* table, int table_width, int ring_pages, void* cache, int cache_dtype,
+                          cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(cache_dtype), "gb_latent_prep: bad dtype");
     GB_REQUIRE(H > 0 && D >= 0 && C > 0 && Rd >= 0 && Rd % 2 == 0 && rot_dims >= 0 && rot_dims <= Rd && rot_dims % 2 == 0,
                "gb_latent_prep: bad sizes heads=%d dim=%d rot_dim=%d kv_rank=%d rotated=%d", H, D, Rd, C, rot_dims);
@@ -146,43 +158,96 @@ GB_API int gb_latent_prep(const void* q, long long ldq, const void* dkv, long lo
     GB_REQUIRE(table && cache && ring_pages > 0 && table_width >= 1 && eps > 0.f, "gb_latent_prep: cache missing");
     if (T == 0) return 0;
     latent_prep_kernel<<<T, 128, 0, stream>>>(q, ldq, dkv, ldd, dtype, H, D, Rd, C, rot_dims, inv_freq, w, w_dtype, eps, qa, lda,
-                                              seq_of, pos, table, table_width, ring_pages, cache, cache_dtype);
+                                              qa_stride, qa_off, row_out, seq_of, pos, table, table_width, ring_pages, cache, cache_dtype);
     GB_LAUNCH_OK("gb_latent_prep");
+    return 0;
+}
+
+// Keys and values per head of a prompt, laid out as pages for the tiled attention kernel: for token t of
+// sequence b at position p (page table[b][p / 64], place p % 64),
+//   K[page, h, place, :] = [kv[t, h*D : (h+1)*D], row[t, C : C + Rd]]    (the head's own part, the shared rotated part)
+//   V[page, h, place, :] = kv[t, H*D + h*Dv : H*D + (h+1)*Dv]
+// kv [T, H*D + H*Dv] is the product of the latent rows with the two up-projections, row [T, C + Rd] the
+// rows that latent_prep wrote.  One block per token.
+__global__ void pack_latent_heads_kernel(const __nv_bfloat16* __restrict__ kv, long long ldkv,
+                                         const __nv_bfloat16* __restrict__ row, int H, int D, int Rd, int Dv, int C,
+                                         const int* __restrict__ seq_of, const int* __restrict__ pos,
+                                         const int* __restrict__ table, int table_width, __nv_bfloat16* __restrict__ K,
+                                         __nv_bfloat16* __restrict__ V) {
+    const int t = blockIdx.x;
+    const int b = seq_of[t];
+    if (b < 0) return;
+    const int p = pos[t];
+    const int page = table[size_t(b) * table_width + (p >> GB_PAGE_SHIFT)], place = p & (GB_PAGE - 1);
+    const int hk = D + Rd;
+    const __nv_bfloat16* kvr = kv + size_t(t) * ldkv;
+    const __nv_bfloat16* rr = row + size_t(t) * (C + Rd) + C;
+    for (int idx = threadIdx.x; idx < H * hk; idx += blockDim.x) {
+        const int h = idx / hk, d = idx - h * hk;
+        K[((size_t(page) * H + h) * GB_PAGE + place) * hk + d] = d < D ? kvr[h * D + d] : rr[d - D];
+    }
+    for (int idx = threadIdx.x; idx < H * Dv; idx += blockDim.x) {
+        const int h = idx / Dv, d = idx - h * Dv;
+        V[((size_t(page) * H + h) * GB_PAGE + place) * Dv + d] = kvr[size_t(H) * D + idx];
+    }
+}
+
+GB_API int gb_pack_latent_heads(const void* kv, long long ldkv, const void* row, int T, int H, int D, int Rd, int Dv, int C,
+                                const int* seq_of, const int* pos, const int* table, int table_width, void* K, void* V,
+                                cudaStream_t stream) {
+    GB_REQUIRE(H > 0 && D > 0 && Rd >= 0 && Dv > 0 && C > 0 && table_width > 0, "gb_pack_latent_heads: bad sizes");
+    if (T == 0) return 0;
+    pack_latent_heads_kernel<<<T, 256, 0, stream>>>((const __nv_bfloat16*)kv, ldkv, (const __nv_bfloat16*)row, H, D, Rd, Dv, C,
+                                                    seq_of, pos, table, table_width, (__nv_bfloat16*)K, (__nv_bfloat16*)V);
+    GB_LAUNCH_OK("gb_pack_latent_heads");
     return 0;
 }
 
 // --------------------------------------------------- a product per head
 // out[t, h*os + o] = sum_i x[t, h*xs + i] * W[h, i, o] for o < O: every head has a matrix [I, O] of its own
-// (row-major, heads one after the other).  32-bit FMAs in ascending i, one thread per output column and
-// tile of HM_TOKENS tokens, so a token's result does not depend on the batch.
+// (row-major, heads one after the other).  32-bit FMAs.  A block takes HM_TOKENS tokens, one head and 32
+// output columns; its four warps take a quarter of the inputs each (in ascending i) and the quarters are
+// added in warp order, so a token's result depends on neither the batch nor timing.
 constexpr int HM_TOKENS = 8;
 
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(128) head_matmul_kernel(const TX* __restrict__ x, long long ldx, int xs,
                                                           const TW* __restrict__ W, int I, int O, void* __restrict__ out,
                                                           int out_dtype, long long ldo, int os, int T) {
-    extern __shared__ float xt[];                     // [HM_TOKENS][I]
+    extern __shared__ float xt[];                     // [HM_TOKENS][I], then [4][HM_TOKENS][32] partial sums
+    float* part = xt + HM_TOKENS * I;
     const int t0 = blockIdx.x * HM_TOKENS, h = blockIdx.y;
-    const int o = blockIdx.z * 128 + threadIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int o = blockIdx.z * 32 + lane;
     const int nt = min(HM_TOKENS, T - t0);
     for (int idx = threadIdx.x; idx < HM_TOKENS * I; idx += 128) {
         const int tt = idx / I, i = idx - tt * I;
         xt[idx] = tt < nt ? gb_to_float(x[size_t(t0 + tt) * ldx + size_t(h) * xs + i]) : 0.f;
     }
     __syncthreads();
-    if (o >= O) return;
     float acc[HM_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = 0.f;
-    const TW* wp = W + size_t(h) * I * O + o;
-    for (int i = 0; i < I; ++i) {
-        const float wv = gb_to_float(wp[size_t(i) * O]);
+    const int per = (I + 3) / 4, i0 = warp * per, i1 = min(I, i0 + per);
+    if (o < O) {
+        const TW* wp = W + size_t(h) * I * O + o;
+        for (int i = i0; i < i1; ++i) {
+            const float wv = gb_to_float(wp[size_t(i) * O]);
 #pragma unroll
-        for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = fmaf(xt[tt * I + i], wv, acc[tt]);
+            for (int tt = 0; tt < HM_TOKENS; ++tt) acc[tt] = fmaf(xt[tt * I + i], wv, acc[tt]);
+        }
     }
 #pragma unroll
-    for (int tt = 0; tt < HM_TOKENS; ++tt)
-        if (tt < nt) gb_store(out, out_dtype, size_t(t0 + tt) * ldo + size_t(h) * os + o, acc[tt]);
+    for (int tt = 0; tt < HM_TOKENS; ++tt) part[(warp * HM_TOKENS + tt) * 32 + lane] = acc[tt];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < HM_TOKENS * 32; idx += 128) {
+        const int tt = idx >> 5, ol = idx & 31, oo = blockIdx.z * 32 + ol;
+        if (tt < nt && oo < O) {
+            const float v = ((part[(0 * HM_TOKENS + tt) * 32 + ol] + part[(1 * HM_TOKENS + tt) * 32 + ol]) +
+                             part[(2 * HM_TOKENS + tt) * 32 + ol]) + part[(3 * HM_TOKENS + tt) * 32 + ol];
+            gb_store(out, out_dtype, size_t(t0 + tt) * ldo + size_t(h) * os + oo, v);
+        }
+    }
 }
 
 // x: head h's I inputs start at column h*xs of a row (rows ldx apart); out: its O results start at column h*os.
@@ -190,10 +255,11 @@ GB_API int gb_head_matmul(const void* x, int x_dtype, long long ldx, int xs, con
                           void* out, int out_dtype, long long ldo, int os, int T, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(x_dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(out_dtype), "gb_head_matmul: bad dtype");
     GB_REQUIRE(H > 0 && H <= 65535 && I > 0 && O > 0 && xs >= I && os >= O, "gb_head_matmul: bad sizes heads=%d in=%d out=%d", H, I, O);
-    const size_t smem = size_t(HM_TOKENS) * I * sizeof(float);
-    GB_REQUIRE(smem <= 48 * 1024, "gb_head_matmul: %d inputs per head exceed %d", I, 48 * 1024 / (4 * HM_TOKENS));
+    const size_t smem = (size_t(HM_TOKENS) * I + 4 * HM_TOKENS * 32) * sizeof(float);
+    GB_REQUIRE(smem <= 48 * 1024, "gb_head_matmul: %d inputs per head exceed %d", I, (48 * 1024 / 4 - 4 * HM_TOKENS * 32) / HM_TOKENS);
     if (T == 0) return 0;
-    dim3 grid((T + HM_TOKENS - 1) / HM_TOKENS, H, (O + 127) / 128);
+    dim3 grid((T + HM_TOKENS - 1) / HM_TOKENS, H, (O + 31) / 32);
+    GB_REQUIRE(grid.z <= 65535, "gb_head_matmul: too many outputs per head (%d)", O);
 #define HM_LAUNCH(TX, TW)                                                                                             \
     head_matmul_kernel<TX, TW><<<grid, 128, smem, stream>>>((const TX*)x, ldx, xs, (const TW*)W, I, O, out, out_dtype, ldo, os, T)
     if (x_dtype == GB_F32 && w_dtype == GB_F32) HM_LAUNCH(float, float);

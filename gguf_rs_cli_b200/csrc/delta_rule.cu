@@ -12,20 +12,22 @@
 // ------------------------------------------------- short convolution + SiLU
 // out[t, c] = silu(sum_j taps[c, j] * in[t - (K-1-j), c]); rows before the step's first token come from
 // the sequence's carried inputs state[slot, 0..K-2, c] (oldest first; zero for a sequence that starts).
-// One block per token.  Padding tokens (seq_of < 0) give zeros.
+// blockIdx.x is the token, blockIdx.y a slice of blockDim.x channels.  Padding tokens (seq_of < 0) give zeros.
 __global__ void short_conv_silu_kernel(const void* __restrict__ xin, int dtype, long long ldx, int C, int K,
                                        const void* __restrict__ taps, int taps_dtype, const float* __restrict__ state,
                                        const int* __restrict__ seq_of, const int* __restrict__ cu,
                                        const int* __restrict__ slots, void* __restrict__ out, long long ldo) {
     const int t = blockIdx.x;
     const int b = seq_of[t];
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
     if (b < 0) {
-        for (int c = threadIdx.x; c < C; c += blockDim.x) gb_store(out, dtype, size_t(t) * ldo + c, 0.f);
+        gb_store(out, dtype, size_t(t) * ldo + c, 0.f);
         return;
     }
     const int first = cu[b], i = t - first, slot = slots[b];
     const float* st = state + size_t(slot) * (K - 1) * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    {
         float acc = 0.f;
         for (int j = 0; j < K; ++j) {
             const int src = i - (K - 1 - j);
@@ -38,7 +40,8 @@ __global__ void short_conv_silu_kernel(const void* __restrict__ xin, int dtype, 
 }
 
 // After the convolution: the sequence's carried inputs become the last K-1 inputs including this step's.
-// One block per sequence; a thread owns a channel, reads all it needs and then writes.
+// blockIdx.x is the sequence, blockIdx.y a slice of channels; a thread owns a channel, reads all it needs and
+// then writes.
 constexpr int CONV_MAX_TAPS = 16;
 
 __global__ void short_conv_carry_kernel(const void* __restrict__ xin, int dtype, long long ldx, int C, int K,
@@ -49,7 +52,8 @@ __global__ void short_conv_carry_kernel(const void* __restrict__ xin, int dtype,
     if (slot < 0 || n <= 0) return;
     const int first = cu[b];
     float* st = state + size_t(slot) * (K - 1) * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c < C) {
         float keep[CONV_MAX_TAPS - 1];
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
@@ -74,11 +78,12 @@ GB_API int gb_short_conv_silu(const void* xin, int dtype, long long ldx, int T, 
                C, K, CONV_MAX_TAPS);
     GB_REQUIRE(K == 1 || state, "gb_short_conv_silu: a convolution of %d taps needs the carried inputs", K);
     if (T == 0) return 0;
-    const int threads = C >= 1024 ? 256 : 128;
-    short_conv_silu_kernel<<<T, threads, 0, stream>>>(xin, dtype, ldx, C, K, taps, taps_dtype, state, seq_of, cu, slots, out, ldo);
+    const int threads = 128, slices = (C + threads - 1) / threads;
+    GB_REQUIRE(slices <= 65535, "gb_short_conv_silu: too many channels (%d)", C);
+    short_conv_silu_kernel<<<dim3(T, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, taps, taps_dtype, state, seq_of, cu, slots, out, ldo);
     GB_LAUNCH_OK("gb_short_conv_silu");
     if (K > 1 && B > 0) {
-        short_conv_carry_kernel<<<B, threads, 0, stream>>>(xin, dtype, ldx, C, K, state, cu, slots, qlens);
+        short_conv_carry_kernel<<<dim3(B, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, state, cu, slots, qlens);
         GB_LAUNCH_OK("gb_short_conv_silu (carry)");
     }
     return 0;

@@ -4,8 +4,8 @@
 // For each output row r (source row s = rows ? rows[r] : r):
 //   v = x[s,:] + sum_d delta[d][s,:]            (32-bit sum; written back to x when write_x)
 //   out[r,i] = tanh(alpha * v[i]) * w[i] + b[i]
-// No statistic of the row is taken, so nothing crosses threads.  All arithmetic is 32-bit with
-// the accurate tanhf.
+// No statistic of the row is taken, so nothing crosses threads: blockIdx.x is the row, blockIdx.y a slice
+// of it.  All arithmetic is 32-bit with the accurate tanhf.
 #include "common.cuh"
 
 __global__ void add_dyt_kernel(float* __restrict__ x, const void* __restrict__ delta, int delta_dtype, int n_delta,
@@ -15,7 +15,7 @@ __global__ void add_dyt_kernel(float* __restrict__ x, const void* __restrict__ d
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = x + size_t(s) * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < E; i += gridDim.y * blockDim.x) {
         float v = xr[i];
         for (int d = 0; d < n_delta; ++d) v += gb_load(delta, delta_dtype, d * delta_stride + size_t(s) * E + i);
         if (write_x && n_delta) xr[i] = v;
@@ -30,8 +30,10 @@ GB_API int gb_add_dyt(float* x, const void* delta, int delta_dtype, int n_delta,
     GB_REQUIRE(n_delta == 0 || (delta && gb_is_dtype(delta_dtype)), "gb_add_dyt: bad delta");
     GB_REQUIRE(E > 0 && n_rows >= 0 && w && b, "gb_add_dyt: bad sizes E=%d rows=%d", E, n_rows);
     if (n_rows == 0) return 0;
-    const int threads = E >= 1024 ? 256 : 128;
-    add_dyt_kernel<<<n_rows, threads, 0, stream>>>(x, delta, delta_dtype, n_delta, size_t(delta_stride), rows, E, w, b,
+    const int threads = 128;
+    int slices = (E + threads - 1) / threads;
+    slices = slices > 16 ? 16 : slices;
+    add_dyt_kernel<<<dim3(n_rows, slices), threads, 0, stream>>>(x, delta, delta_dtype, n_delta, size_t(delta_stride), rows, E, w, b,
                                                    w_dtype, alpha, out, out_dtype, write_x);
     GB_LAUNCH_OK("gb_add_dyt");
     return 0;

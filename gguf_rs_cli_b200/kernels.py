@@ -200,19 +200,42 @@ def qk_norm_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[tor
 
 
 def latent_prep(q: torch.Tensor, dkv: torch.Tensor, n_heads: int, dim: int, rot_dim: int, kv_rank: int, rot_dims: int,
-                inv_freq: Optional[torch.Tensor], weight: torch.Tensor, eps: float, qa: torch.Tensor, seq_of: torch.Tensor,
-                pos: torch.Tensor, table: torch.Tensor, ring_pages: int, cache: torch.Tensor) -> None:
+                inv_freq: Optional[torch.Tensor], weight: torch.Tensor, eps: float, qa: Optional[torch.Tensor],
+                seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int, cache: torch.Tensor,
+                row_out: Optional[torch.Tensor] = None) -> None:
     """Latent attention in front of the attention kernel: dkv [T, kv_rank + rot_dim] gives the cache row
-    (RMS-normed latent, rotated shared key part); the heads' rotated query parts go to qa [T, heads*(kv_rank +
-    rot_dim)] behind the kv_rank entries that head_matmul fills."""
-    _cuda(q, dkv, inv_freq, weight, qa, seq_of, pos, table, cache)
+    (RMS-normed latent, rotated shared key part; also copied to row_out [T, kv_rank + rot_dim] when given); the
+    heads' rotated query parts go to qa [T, heads*(kv_rank + rot_dim)] behind the kv_rank entries that
+    head_matmul fills, or, with qa None, are rotated in place in q."""
+    _cuda(q, dkv, inv_freq, weight, qa, seq_of, pos, table, cache, row_out)
     T = q.shape[0]
-    assert q.stride(1) == 1 and dkv.stride(1) == 1 and qa.stride(1) == 1 and q.dtype == dkv.dtype == qa.dtype
+    assert q.stride(1) == 1 and dkv.stride(1) == 1 and q.dtype == dkv.dtype
     assert q.shape[1] == n_heads * (dim + rot_dim) and dkv.shape[1] == kv_rank + rot_dim
-    assert qa.shape == (T, n_heads * (kv_rank + rot_dim)) and cache.shape[-1] == kv_rank + rot_dim and weight.numel() == kv_rank
+    assert cache.shape[-1] == kv_rank + rot_dim and weight.numel() == kv_rank
+    if qa is None:
+        qa, stride, off = q, dim + rot_dim, dim
+    else:
+        stride, off = kv_rank + rot_dim, kv_rank
+        assert qa.shape == (T, n_heads * (kv_rank + rot_dim)) and qa.stride(1) == 1 and qa.dtype == q.dtype
+    assert row_out is None or (row_out.shape == (T, kv_rank + rot_dim) and row_out.is_contiguous() and row_out.dtype == q.dtype)
     call("gb_latent_prep", ptr(q), q.stride(0), ptr(dkv), dkv.stride(0), dtype_code(q), T, n_heads, dim, rot_dim, kv_rank,
-         rot_dims, ptr(inv_freq), ptr(weight), dtype_code(weight), float(eps), ptr(qa), qa.stride(0), ptr(seq_of), ptr(pos),
-         ptr(table), table.shape[1], ring_pages, ptr(cache), dtype_code(cache), stream_ptr())
+         rot_dims, ptr(inv_freq), ptr(weight), dtype_code(weight), float(eps), ptr(qa), qa.stride(0), stride, off,
+         ptr(row_out), ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(cache), dtype_code(cache), stream_ptr())
+
+
+def pack_latent_heads(kv: torch.Tensor, row: torch.Tensor, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
+                      seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, k_pages: torch.Tensor,
+                      v_pages: torch.Tensor) -> None:
+    """Per-head keys [pages, heads, 64, dim + rot_dim] (the head's up-projected part, then the shared rotated part
+    of `row`) and values [pages, heads, 64, vdim] of a prompt's tokens, at the pages `table` names."""
+    _cuda(kv, row, seq_of, pos, table, k_pages, v_pages)
+    T = kv.shape[0]
+    assert kv.dtype == row.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16 and kv.stride(1) == 1 and row.is_contiguous()
+    assert kv.shape[1] == n_heads * (dim + vdim) and row.shape == (T, kv_rank + rot_dim)
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape[1:] == (n_heads, 64, dim + rot_dim)
+    assert v_pages.shape[1:] == (n_heads, 64, vdim) and table.dim() == 2
+    call("gb_pack_latent_heads", ptr(kv), kv.stride(0), ptr(row), T, n_heads, dim, rot_dim, vdim, kv_rank, ptr(seq_of), ptr(pos),
+         ptr(table), table.shape[1], ptr(k_pages), ptr(v_pages), stream_ptr())
 
 
 def head_matmul(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int) -> torch.Tensor:
@@ -369,6 +392,11 @@ def decode_split_class(max_kv: int) -> int:
     return _split_class(((max_kv + 63) // 64) // 4)
 
 
+def decode_split_class_cuda(max_kv: int) -> int:
+    """The same for the CUDA-core decode kernel, whose splits (decode_splits with mma False) follow an eighth of the pages."""
+    return _split_class(((max_kv + 63) // 64) // 8)
+
+
 def decode_splits(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int, mma: bool) -> int:
     """Splits of each sequence's pages for a decode step; a function of the step's class (decode_split_class)
     and its CTAs, so that all steps of a captured graph split alike.
@@ -385,7 +413,7 @@ def decode_splits(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int, 
     ctas = T * n_kv_heads * ((group + tile - 1) // tile)
     pages = (max_kv + 63) // 64
     if not mma:
-        return max(1, min(_split_class(pages // 8), 32, (2 * sms) // ctas))
+        return max(1, min(decode_split_class_cuda(max_kv), 32, (2 * sms) // ctas))
     cls = decode_split_class(max_kv)                       # a quarter of the pages, rounded down to a class
     if ctas > sms or cls < 4:
         return 1
@@ -467,15 +495,17 @@ def attention_prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor, head_d
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       tiles: torch.Tensor, cu: torch.Tensor, starts: torch.Tensor, qlens: torch.Tensor,
                       table: torch.Tensor, ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int,
-                      scale: float, tc: Optional[bool] = None) -> torch.Tensor:
+                      scale: float, tc: Optional[bool] = None, exact: bool = False) -> torch.Tensor:
     """Many tokens per sequence over the bf16 cache (which already holds their keys and
     values), flash style.  tc: both products on tcgen05 with S and PV in TMEM (the default where it
-    fits), else on mma.sync; both take head sizes 64 and 128."""
+    fits), else on mma.sync; both take head sizes 64 and 128.  exact (mma.sync kernel only): the
+    attention weights stay 32-bit, split into three bfloat16 terms for the product with the values."""
     _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (q.shape[0], n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
     if tc is None:
-        tc = attention_prefill_tc_supported(q, kcache, head_dim)
+        tc = attention_prefill_tc_supported(q, kcache, head_dim) and not exact
+    assert not (tc and exact)
     if tc:
         assert kcache.is_contiguous() and vcache.is_contiguous()
         call("gb_attention_prefill_tc", ptr(q), q.stride(0), ptr(out), out.stride(0), q.shape[0], n_heads, n_kv_heads,
@@ -484,7 +514,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
         return out
     call("gb_attention_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), n_heads, n_kv_heads, head_dim, ptr(tiles),
          tiles.numel() // 2, ptr(cu), ptr(starts), ptr(qlens), ptr(table), table.shape[1], ring_pages, ptr(kcache),
-         ptr(vcache), int(window or 0), float(scale), stream_ptr())
+         ptr(vcache), int(window or 0), float(scale), int(bool(exact)), stream_ptr())
     return out
 
 

@@ -147,7 +147,8 @@ _SIGNATURES = {
     "gb_delta_rule": [_P, _P, _P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _P],
     "gb_qk_norm_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P],
-    "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _P, _P, _P, _I, _I, _P, _I, _P],
+    "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _P],
+    "gb_pack_latent_heads": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
     "gb_head_matmul": [_P, _I, _L, _I, _P, _I, _I, _I, _I, _P, _I, _L, _I, _I, _P],
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
     "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P],
@@ -169,7 +170,7 @@ _SIGNATURES = {
     "gb_gemm_tc_set_stamps": [_P, _I, _I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
-    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _P],
+    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P],
     "gb_attention_prefill_supported": [_I, _I, _I],
     "gb_attention_prefill_tile": [],
     "gb_attention_prefill_tc": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _L, _I, _F, _P],

@@ -97,15 +97,27 @@ class Attention(Part):
 
     def plan(self, batch: HostBatch):
         """Prompts: the list of query tiles (sequence row, first query) that the prefill kernel's CTAs take."""
-        if batch.decode or self.exact:
+        if batch.decode or (self.exact and not self._exact_tiled()):
             return {}
         return {"tiles": kernels.attention_prefill_tiles(batch.qlens)}
+
+    def _exact_tiled(self) -> bool:
+        """Whether prompts of the exact path take the tiled kernel (bfloat16, keys and values of 64 or 128 entries
+        both) with 32-bit attention weights; other sizes and the 32-bit mode take the general kernel."""
+        return self.dtype == torch.bfloat16 and self.vd == self.hd and self.hd in (64, 128)
+
+    def _exact_decode(self) -> bool:
+        """Whether single tokens of the exact path take the CUDA-core decode kernel (32-bit weights; bfloat16, keys
+        and values of one size that is a multiple of 16 up to 256)."""
+        return self.dtype == torch.bfloat16 and self.vd == self.hd and self.hd % 16 == 0 and self.hd <= 256
 
     def graph_class(self, batch: HostBatch):
         """The decode kernel splits each sequence's pages over CTAs by a rule of the longest sequence; steps
         of one class launch the same grid and may share a captured graph."""
         if self.exact:
-            return ()                                  # one block per token and head, whatever the lengths
+            # the general kernel: one block per token and head, whatever the lengths; the CUDA-core decode kernel
+            # splits each sequence's pages by a rule of the longest sequence
+            return ("cuda", kernels.decode_split_class_cuda(batch.max_kv)) if self._exact_decode() else ()
         return kernels.decode_split_class(min(batch.max_kv, self.window) if self.window else batch.max_kv)
 
     def absorb_input_norm(self, weight: torch.Tensor) -> bool:
@@ -153,8 +165,17 @@ class Attention(Part):
         kernels.qk_norm_kv_write(q, k, v, nh, nkv, hd, vd, self.qk_norm_eps is not None, self.qk_norm_eps or 1.0,
                                  self.temp_coef, self.temp_every, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v)
         out = ctx.ws.get("attn.out", (qkv.shape[0], nh * vd), ctx.dtype)
-        kernels.attention_generic(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
-                                  self.window or 0, self.scale, v_dim=vd)
+        tiles = ctx.plan_of(self).get("tiles")
+        if not ctx.decode and tiles is not None and self._exact_tiled() and kernels.attention_prefill_supported(q, run.k, hd):
+            kernels.attention_prefill(q, out, nh, nkv, hd, tiles, ctx.cu, ctx.starts, ctx.qlens, table, run.ring_pages,
+                                      run.k, run.v, self.window or 0, self.scale, tc=False, exact=True)
+        elif ctx.decode and self._exact_decode() and kernels.attention_decode_supported(q, run.k, hd):
+            kernels.attention_decode(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
+                                     self.window or 0, self.scale, mma=False,
+                                     max_kv=min(ctx.max_kv, self.window) if self.window else ctx.max_kv)
+        else:
+            kernels.attention_generic(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
+                                      self.window or 0, self.scale, v_dim=vd)
         ctx.mark("attention")
         term = self.o(out, ctx, residual=residual)
         ctx.mark("o")

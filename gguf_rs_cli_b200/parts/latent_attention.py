@@ -7,6 +7,11 @@ with W_uk and W_uv are moved to the query's side: q' = W_uk^T q_plain lives in t
 head's score is [q', q_rot] . [c, k_rot], the mix of values is the mix of latent rows, and W_uv is applied
 to that mix once per token.  The attention kernel then sees one key/value head of kv_rank + rot_dim entries
 whose first kv_rank entries are also its values.  Scores, softmax and mix run in 32-bit.
+
+Prompts that start their sequences take the other order where the sizes allow it (bfloat16, dim + rot_dim
+= vdim = 64 or 128): the step's latent rows are multiplied with W_uk and W_uv in one tensor-core product,
+the per-head keys [W_uk c, k_rot] and values are laid out as pages of the step's own, and the tiled
+attention kernel runs over them with 32-bit weights; the cache still receives the latent rows only.
 """
 from __future__ import annotations
 
@@ -17,7 +22,7 @@ import torch
 from .. import kernels
 from ..cache.cache import KVSpec
 from ..weights.loader import TensorRequest, WeightStore
-from .base import Part, RunView, StepContext
+from .base import HostBatch, Part, RunView, StepContext
 from .linear import Linear
 from .registry import register_mixer
 
@@ -69,7 +74,29 @@ class LatentAttention(Part):
         self.norm_weight = norm
         self.uk = uk.reshape(H, D, C).contiguous()                           # q' = q_plain W_uk[h]: [in D, out C]
         self.uv_t = uv.reshape(H, Dv, C).transpose(1, 2).contiguous()        # value = mix W_uv[h]^T: [in C, out Dv]
+        self.kv_up = Linear(torch.cat([uk, uv.to(uk.dtype)], dim=0).contiguous(), name="latent.kv") if self._tiled() else None
         self.o = Linear(o, name="latent.o")
+
+    def _tiled(self) -> bool:
+        """Whether prompts can take the tiled attention kernel over per-head keys and values."""
+        return self.dtype == torch.bfloat16 and self.D + self.R == self.Dv and self.Dv in (64, 128)
+
+    # ---- planning on the host
+    def plan_key(self):
+        return ("latent_attention", self.D, self.R, self.Dv, self._tiled())
+
+    def plan(self, batch: HostBatch):
+        """Prompts that start their sequences, where the tiled kernel fits: its list of query tiles, and a page table
+        of the step's own (sequence b's tokens lie in pages of their own, numbered from 0 on across the step)."""
+        if batch.decode or not self._tiled() or any(batch.starts):
+            return {}
+        width = max((n + 63) // 64 for n in batch.qlens)
+        table, base = [], 0
+        for n in batch.qlens:
+            pages = (n + 63) // 64
+            table += list(range(base, base + pages)) + [0] * (width - pages)
+            base += pages
+        return {"tiles": kernels.attention_prefill_tiles(batch.qlens), "pages": table, "n_pages": [base]}
 
     accepts_residual = True
     graph_class = ()              # one block per token and head, whatever the lengths
@@ -82,6 +109,26 @@ class LatentAttention(Part):
         q, dkv = proj[:, :H * (D + R)], proj[:, self.off_dkv:self.off_dkv + C + R]
         table = ctx.tables[run.group]
         pos = self.position
+        plan = ctx.plan_of(self)
+        if not ctx.decode and "pages" in plan and kernels.attention_prefill_supported(q, run.k, D + R):
+            # per-head keys and values of this step's tokens as pages of the step's own
+            row = ctx.ws.get("latent.row", (T, C + R), ctx.dtype)
+            kernels.latent_prep(q, dkv, H, D, R, C, 0 if pos is None else pos.rotary_dim, None if pos is None else pos.inv_freq,
+                                self.norm_weight, self.p["eps"], None, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k,
+                                row_out=row)
+            kv = self.kv_up(row[:, :C], ctx)
+            own = plan["pages"].view(ctx.B, -1)
+            n_pages = sum((n + 63) // 64 for n in ctx.host["qlens"])
+            k_pages = ctx.ws.get("latent.k_pages", (n_pages, H, 64, D + R), ctx.dtype)
+            v_pages = ctx.ws.get("latent.v_pages", (n_pages, H, 64, Dv), ctx.dtype)
+            kernels.pack_latent_heads(kv, row, H, D, R, Dv, C, ctx.seq_of, ctx.pos, own, k_pages, v_pages)
+            values = ctx.ws.get("latent.values", (T, H * Dv), ctx.dtype)
+            kernels.attention_prefill(q, values, H, H, D + R, plan["tiles"], ctx.cu, ctx.starts, ctx.qlens, own, 1 << 20,
+                                      k_pages, v_pages, 0, float(self.p["scale"]), tc=False, exact=True)
+            ctx.mark("attention")
+            term = self.o(values, ctx, residual=residual)
+            ctx.mark("o")
+            return term
         qa = ctx.ws.get("latent.qa", (T, H * (C + R)), ctx.dtype)
         kernels.latent_prep(q, dkv, H, D, R, C, 0 if pos is None else pos.rotary_dim, None if pos is None else pos.inv_freq,
                             self.norm_weight, self.p["eps"], qa, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k)
