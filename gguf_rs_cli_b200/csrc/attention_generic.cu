@@ -4,7 +4,7 @@
 // h reads KV head h / (nh/nkv); scores q.k * scale over the positions the token may
 // see (<= its own, and inside the window if there is one); softmax with the maximum
 // subtracted; weighted sum of values.  All in 32-bit with expf.  Keys are taken in
-// blocks of 32 absolute positions, warp w taking blocks w, w+4, ..., and the four
+// blocks of 32 absolute positions, warp w taking blocks w, w+8, ..., and the eight
 // partial results are merged in warp order, so a token's result depends on nothing but
 // its own query and keys.  It is the attention of the 32-bit mode, the twin of the
 // faster kernels in tests, and the path for head sizes those refuse.
@@ -13,7 +13,7 @@
 #include "common.cuh"
 
 constexpr int AG_MAX_HD = 640;
-constexpr int AG_WARPS = 4;
+constexpr int AG_WARPS = 8;
 
 // hd: entries of a query and of a key; hdv: entries of a value (and of a head's result); a value row starts
 // every v_row entries of the value storage, which lets the values be the first hdv entries of the key rows
@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     __syncthreads();
 
     int p = pos[t];
+    const bool vec8 = hd % 8 == 0 && (reinterpret_cast<uintptr_t>(kc) & 15) == 0;     // key rows start on 16 bytes
     int lo = window > 0 ? max(0, p - window + 1) : 0;
     int g = h / (nh / nkv);
     const int* trow = table + size_t(b) * table_width;
@@ -48,13 +49,57 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     for (int c = 0; c < C; ++c) acc[c] = 0.f;
     float m = -INFINITY, l = 0.f;
 
+    // bfloat16 rows that start on 16 bytes: the lanes share each key row in pieces of eight entries (pieces lane,
+    // lane + 32, ...), so that a row is read once and contiguously; shuffles bring the partial sums together.
+    // Other rows: each lane walks its own key's row.  Either way the order of the sums is fixed by the sizes alone.
+    constexpr int QC = (MAX_HD / 8 + 31) / 32;
+    const bool shared_rows = sizeof(TC) == 2 && vec8;
+    const bool pairs = sizeof(TC) == 2 && hdv % 2 == 0 && v_row % 2 == 0 && (reinterpret_cast<uintptr_t>(vc) & 3) == 0;
+    float qr[QC][8];
+    if (shared_rows) {
+#pragma unroll
+        for (int c = 0; c < QC; ++c)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) qr[c][e] = (lane + 32 * c) * 8 < hd ? qs[(lane + 32 * c) * 8 + e] : 0.f;
+    }
+
     for (int kb = (lo >> 5) + warp; kb <= (p >> 5); kb += AG_WARPS) {
         int j = kb * 32 + lane;
         bool valid = j >= lo && j <= p;
         float s = -INFINITY;
         long long off = 0;
-        if (valid) {
-            off = (long long)gb_kv_offset(trow, ring_pages, j, g, nkv, 1);        // the position's row number
+        if (valid) off = (long long)gb_kv_offset(trow, ring_pages, j, g, nkv, 1);        // the position's row number
+        if (shared_rows) {
+            const unsigned live = __ballot_sync(0xffffffffu, valid);
+            for (int jj = 0; jj < 32; jj += 2) {
+                if (!((live >> jj) & 3u)) continue;                                       // neither key is seen (uniform)
+                const long long o0 = __shfl_sync(0xffffffffu, off, jj), o1 = __shfl_sync(0xffffffffu, off, jj + 1);
+                const uint4* k0 = reinterpret_cast<const uint4*>(kc + o0 * hd);
+                const uint4* k1 = reinterpret_cast<const uint4*>(kc + o1 * hd);
+                float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+                for (int c = 0; c < QC; ++c) {
+                    const int piece = lane + 32 * c;
+                    if (piece * 8 < hd) {
+                        const uint4 r0 = k0[piece], r1 = k1[piece];
+                        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&r0);
+                        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 ka = __bfloat1622float2(a2[e]), kb2 = __bfloat1622float2(b2[e]);
+                            d0 = fmaf(qr[c][2 * e], ka.x, d0);
+                            d0 = fmaf(qr[c][2 * e + 1], ka.y, d0);
+                            d1 = fmaf(qr[c][2 * e], kb2.x, d1);
+                            d1 = fmaf(qr[c][2 * e + 1], kb2.y, d1);
+                        }
+                    }
+                }
+                d0 = gb_warp_sum(d0);
+                d1 = gb_warp_sum(d1);
+                if (lane == jj && valid) s = d0 * scale;
+                if (lane == jj + 1 && valid) s = d1 * scale;
+            }
+        } else if (valid) {
             const TC* kr = kc + off * hd;
             float dot = 0.f;
             for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], gb_to_float(kr[d]), dot);
@@ -71,10 +116,23 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
             long long o = __shfl_sync(0xffffffffu, off, jj);
             if (pv != 0.f) {
                 const TC* vr = vc + o * v_row;
+                if (pairs) {
+                    // two bfloat16 values per load: acc[2c], acc[2c+1] belong to entries 64c + 2 lane and the next
+                    const __nv_bfloat162* vr2 = reinterpret_cast<const __nv_bfloat162*>(vr);
 #pragma unroll
-                for (int c = 0; c < C; ++c) {
-                    int d = lane + 32 * c;
-                    if (d < hdv) acc[c] = fmaf(pv, gb_to_float(vr[d]), acc[c]);
+                    for (int c = 0; c < C / 2; ++c) {
+                        if (64 * c + 2 * lane < hdv) {
+                            const float2 vv = __bfloat1622float2(vr2[32 * c + lane]);
+                            acc[2 * c] = fmaf(pv, vv.x, acc[2 * c]);
+                            acc[2 * c + 1] = fmaf(pv, vv.y, acc[2 * c + 1]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        int d = lane + 32 * c;
+                        if (d < hdv) acc[c] = fmaf(pv, gb_to_float(vr[d]), acc[c]);
+                    }
                 }
             }
         }
@@ -82,7 +140,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     }
 #pragma unroll
     for (int c = 0; c < C; ++c) {
-        int d = lane + 32 * c;
+        int d = pairs ? 64 * (c >> 1) + 2 * lane + (c & 1) : lane + 32 * c;
         if (d < hdv) acc_s[warp][d] = acc[c];
     }
     if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }

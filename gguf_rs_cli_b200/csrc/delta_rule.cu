@@ -94,119 +94,176 @@ GB_API int gb_short_conv_silu(const void* xin, int dtype, long long ldx, int T, 
 //   qn = q / sqrt(sum q^2 + 1e-6) * q_scale,  kn = k / sqrt(sum k^2 + 1e-6)
 //   decay_i = exp(-exp(A_log_h) * softplus(a_i + dt_bias_i)),  beta = sigmoid(b)
 //   S_ij <- decay_i S_ij;  u_j = beta (v_j - sum_i S_ij kn_i);  S_ij <- S_ij + kn_i u_j;  o_j = sum_i S_ij qn_i
-// Columns of S do not interact, so a block takes a slice of columns of one (sequence, head): a column is
-// shared by R lanes of a warp (R a power of two), lane r holding rows r, r + R, ...: NR of them in
-// registers; the sums over i end with shuffles over those lanes.  The token's q, k, decay, v and beta are
-// prepared for a few tokens at a time in shared memory by the whole block (rows padded to R*NR entries with
-// zeros, so the inner loops carry no bounds).  The state is read once at the start and written once at the end.
-struct DeltaRuleParams {
+// Two kernels.  The first computes, for all tokens at once, what does not depend on the state: qn and kn per
+// q/k head, decays and beta per head, and the values as 32-bit floats, in rows padded to a multiple of four
+// entries.  The second walks the tokens.  Columns of S do not interact, so a block takes a slice of columns
+// of one (sequence, head): a column is shared by R lanes of a warp (R a power of two), lane r holding the NR
+// rows r*NR .. r*NR + NR - 1 in registers; the sums over i end with shuffles over those lanes.  The prepared
+// rows of a few tokens at a time are copied into shared memory with cp.async, the next chunk while this one
+// is worked on; a lane's share of a row lies NR + 4 floats after its neighbour's, so that 16-byte reads of
+// different lanes fall into different banks.  The state is read once at the start and written once at the end.
+struct DeltaPrepParams {
     const void *q, *k, *v;          // after convolution and SiLU: q, k [T, G*D], v [T, H*Dv], rows `ld` apart
     const void* beta;               // [T, H] before the sigmoid, rows ld_beta apart
     const void* a;                  // [T, H*D] before bias and softplus, rows ld_a apart
     const void *dt_bias, *A_log;    // [H*D], [H]
-    float* state;                   // [slots, H, D, Dv]
-    float* out;                     // [T, H*Dv], rows ldo apart
-    const int *cu, *slots, *qlens;
-    long long ld, ld_beta, ld_a, ldo;
-    int dtype, w_dtype, H, G, D, Dv, R, TC;
+    float* qk;                      // [T, G, 2, DA]: qn, kn
+    float* gb;                      // [T, H, DA + 4]: decays, then beta
+    float* vf;                      // [T, H, VA]
+    long long ld, ld_beta, ld_a;
+    int dtype, w_dtype, H, G, D, Dv, DA, VA;
     float q_scale;
 };
 
+// One warp per item: items 0..H-1 are the heads (decays, beta, values), items H..H+G-1 the q/k heads.
+__global__ void __launch_bounds__(128) delta_prep_kernel(const DeltaPrepParams p) {
+    const int t = blockIdx.x, item = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= p.H + p.G) return;
+    const int D = p.D, DA = p.DA;
+    if (item < p.H) {
+        const int h = item;
+        const float rate = expf(gb_load(p.A_log, p.w_dtype, h));
+        float* g = p.gb + (size_t(t) * p.H + h) * (DA + 4);
+        for (int d = lane; d < DA; d += 32) {
+            float gv = 0.f;
+            if (d < D) {
+                const float z = gb_load(p.a, p.dtype, size_t(t) * p.ld_a + size_t(h) * D + d) +
+                                gb_load(p.dt_bias, p.w_dtype, size_t(h) * D + d);
+                gv = expf(-rate * (z > 20.f ? z : log1pf(expf(z))));
+            }
+            g[d] = gv;
+        }
+        if (lane < 4) g[DA + lane] = lane == 0 ? 1.f / (1.f + expf(-gb_load(p.beta, p.dtype, size_t(t) * p.ld_beta + h))) : 0.f;
+        float* vo = p.vf + (size_t(t) * p.H + h) * p.VA;
+        for (int d = lane; d < p.VA; d += 32) vo[d] = d < p.Dv ? gb_load(p.v, p.dtype, size_t(t) * p.ld + size_t(h) * p.Dv + d) : 0.f;
+    } else {
+        const int g = item - p.H;
+        const size_t row = size_t(t) * p.ld + size_t(g) * D;
+        float sq = 0.f, sk = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float qv = gb_load(p.q, p.dtype, row + d), kv = gb_load(p.k, p.dtype, row + d);
+            sq = fmaf(qv, qv, sq);
+            sk = fmaf(kv, kv, sk);
+        }
+        const float qn = p.q_scale / sqrtf(gb_warp_sum(sq) + 1e-6f), kn = 1.f / sqrtf(gb_warp_sum(sk) + 1e-6f);
+        float* o = p.qk + (size_t(t) * p.G + g) * 2 * DA;
+        for (int d = lane; d < DA; d += 32) {
+            o[d] = d < D ? gb_load(p.q, p.dtype, row + d) * qn : 0.f;
+            o[DA + d] = d < D ? gb_load(p.k, p.dtype, row + d) * kn : 0.f;
+        }
+    }
+}
+
+struct DeltaRuleParams {
+    const float *qk, *gb, *vf;      // what delta_prep_kernel wrote
+    float* state;                   // [slots, H, D, Dv]
+    float* out;                     // [T, H*Dv], rows ldo apart
+    const int *cu, *slots, *qlens;
+    long long ldo;
+    int H, G, D, Dv, DA, VA, R, TC;
+};
+
+__device__ __forceinline__ void dr_cp16(float* dst, const float* src) {
+    unsigned d = unsigned(__cvta_generic_to_shared(dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
 template <int NR>
 __global__ void __launch_bounds__(128) delta_rule_kernel(const DeltaRuleParams p) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.x, h = blockIdx.y;
     const int slot = p.slots[b], n = p.qlens[b];
     if (slot < 0 || n <= 0) return;
-    const int R = p.R, CW = 32 / R, CB = 4 * CW, DP = R * NR, D = p.D, Dv = p.Dv, TC = p.TC;
-    float* qs = sm;
-    float* ks = qs + TC * DP;
-    float* gs = ks + TC * DP;
-    float* vs = gs + TC * DP;
-    float* bs = vs + TC * CB;
+    const int R = p.R, CW = 32 / R, CB = 4 * CW, D = p.D, Dv = p.Dv, DA = p.DA, TC = p.TC;
+    const int RS = R * (NR + 4);                        // floats of one padded row of q, k or decays
+    const int TOK = 3 * RS + 4 + CB;                    // floats per token: q, k, decays, beta (+3), values of the slice
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane / CW, jj = lane - r * CW;
-    const int j = blockIdx.z * CB + warp * CW + jj;
+    const int col0 = blockIdx.z * CB;
+    const int j = col0 + warp * CW + jj;
     const bool col_ok = j < Dv;
     const int g = h / (p.H / p.G);
     float* sp = p.state + (size_t(slot) * p.H + h) * size_t(D) * Dv;
     float S[NR];
 #pragma unroll
     for (int m = 0; m < NR; ++m) {
-        const int i = r + R * m;
+        const int i = r * NR + m;
         S[m] = (i < D && col_ok) ? sp[size_t(i) * Dv + j] : 0.f;
     }
+    for (int i = threadIdx.x; i < 2 * TC * TOK; i += 128) sm[i] = 0.f;      // what no copy reaches stays zero
+    __syncthreads();
     const int t0 = p.cu[b];
-    const float rate = expf(gb_load(p.A_log, p.w_dtype, h));
-    for (int c0 = 0; c0 < n; c0 += TC) {
+    const int q4 = DA / 4, v4 = max(0, min(CB, p.VA - col0)) / 4;         // 16-byte pieces per row
+    auto load_chunk = [&](int c0, int buf) {
         const int nt = min(TC, n - c0);
-        __syncthreads();                                   // the chunk before has been consumed
-        for (int tt = warp; tt < nt; tt += 4) {
+        float* base = sm + buf * TC * TOK;
+        const int per = 3 * q4 + 1 + v4;
+        for (int idx = threadIdx.x; idx < nt * per; idx += 128) {
+            const int tt = idx / per, e = idx - tt * per;
             const size_t t = size_t(t0 + c0 + tt);
-            const size_t row = t * p.ld + size_t(g) * D;
-            float sq = 0.f, sk = 0.f;
-            for (int d = lane; d < DP; d += 32) {
-                float qv = 0.f, kv = 0.f, gv = 0.f;
-                if (d < D) {
-                    qv = gb_load(p.q, p.dtype, row + d);
-                    kv = gb_load(p.k, p.dtype, row + d);
-                    const float z = gb_load(p.a, p.dtype, t * p.ld_a + size_t(h) * D + d) +
-                                    gb_load(p.dt_bias, p.w_dtype, size_t(h) * D + d);
-                    const float soft = z > 20.f ? z : log1pf(expf(z));
-                    gv = expf(-rate * soft);
-                }
-                qs[tt * DP + d] = qv;
-                ks[tt * DP + d] = kv;
-                gs[tt * DP + d] = gv;
-                sq = fmaf(qv, qv, sq);
-                sk = fmaf(kv, kv, sk);
+            float* row = base + tt * TOK;
+            if (e < 2 * q4) {
+                const int which = e / q4, k4 = e - which * q4, i = 4 * k4;
+                dr_cp16(row + which * RS + (i / NR) * (NR + 4) + (i % NR), p.qk + ((t * p.G + g) * 2 + which) * DA + i);
+            } else if (e < 3 * q4) {
+                const int i = 4 * (e - 2 * q4);
+                dr_cp16(row + 2 * RS + (i / NR) * (NR + 4) + (i % NR), p.gb + (t * p.H + h) * (DA + 4) + i);
+            } else if (e == 3 * q4) {
+                dr_cp16(row + 3 * RS, p.gb + (t * p.H + h) * (DA + 4) + DA);
+            } else {
+                const int i = 4 * (e - 3 * q4 - 1);
+                dr_cp16(row + 3 * RS + 4 + i, p.vf + (t * p.H + h) * p.VA + col0 + i);
             }
-            sq = gb_warp_sum(sq);
-            sk = gb_warp_sum(sk);
-            const float qn = p.q_scale / sqrtf(sq + 1e-6f), kn = 1.f / sqrtf(sk + 1e-6f);
-            for (int d = lane; d < DP; d += 32) {          // each lane rescales what it wrote itself
-                qs[tt * DP + d] *= qn;
-                ks[tt * DP + d] *= kn;
-            }
-            if (lane == 0) bs[tt] = 1.f / (1.f + expf(-gb_load(p.beta, p.dtype, t * p.ld_beta + h)));
         }
-        for (int idx = threadIdx.x; idx < nt * CB; idx += 128) {
-            const int tt = idx / CB, cj = idx - tt * CB;
-            const int col = blockIdx.z * CB + cj;
-            vs[idx] = col < Dv ? gb_load(p.v, p.dtype, size_t(t0 + c0 + tt) * p.ld + size_t(h) * Dv + col) : 0.f;
-        }
+    };
+    load_chunk(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    int buf = 0;
+    for (int c0 = 0; c0 < n; c0 += TC, buf ^= 1) {
+        const int nt = min(TC, n - c0);
+        if (c0 + TC < n) load_chunk(c0 + TC, buf ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
+        const float* base = sm + buf * TC * TOK;
         for (int tt = 0; tt < nt; ++tt) {
-            const float* qq = qs + tt * DP + r;
-            const float* kk = ks + tt * DP + r;
-            const float* gg = gs + tt * DP + r;
-            float d0 = 0.f, d1 = 0.f;
+            const float* row = base + tt * TOK;
+            const float4* qq = reinterpret_cast<const float4*>(row + r * (NR + 4));
+            const float4* kk = reinterpret_cast<const float4*>(row + RS + r * (NR + 4));
+            const float4* gg = reinterpret_cast<const float4*>(row + 2 * RS + r * (NR + 4));
+            float4 kr[NR / 4];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < NR; m += 2) {
-                S[m] *= gg[R * m];
-                d0 = fmaf(S[m], kk[R * m], d0);
-                S[m + 1] *= gg[R * (m + 1)];
-                d1 = fmaf(S[m + 1], kk[R * (m + 1)], d1);
+            for (int m = 0; m < NR / 4; ++m) {
+                const float4 gv = gg[m];
+                kr[m] = kk[m];
+                S[4 * m] *= gv.x;     d0 = fmaf(S[4 * m], kr[m].x, d0);
+                S[4 * m + 1] *= gv.y; d1 = fmaf(S[4 * m + 1], kr[m].y, d1);
+                S[4 * m + 2] *= gv.z; d2 = fmaf(S[4 * m + 2], kr[m].z, d2);
+                S[4 * m + 3] *= gv.w; d3 = fmaf(S[4 * m + 3], kr[m].w, d3);
             }
-            float dot = d0 + d1;
+            float dot = (d0 + d1) + (d2 + d3);
             for (int off = CW; off < 32; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-            const float u = bs[tt] * (vs[tt * CB + warp * CW + jj] - dot);
-            float o0 = 0.f, o1 = 0.f;
+            const float u = row[3 * RS] * (row[3 * RS + 4 + warp * CW + jj] - dot);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < NR; m += 2) {
-                S[m] = fmaf(kk[R * m], u, S[m]);
-                o0 = fmaf(S[m], qq[R * m], o0);
-                S[m + 1] = fmaf(kk[R * (m + 1)], u, S[m + 1]);
-                o1 = fmaf(S[m + 1], qq[R * (m + 1)], o1);
+            for (int m = 0; m < NR / 4; ++m) {
+                const float4 qv = qq[m];
+                S[4 * m] = fmaf(kr[m].x, u, S[4 * m]);         o0 = fmaf(S[4 * m], qv.x, o0);
+                S[4 * m + 1] = fmaf(kr[m].y, u, S[4 * m + 1]); o1 = fmaf(S[4 * m + 1], qv.y, o1);
+                S[4 * m + 2] = fmaf(kr[m].z, u, S[4 * m + 2]); o2 = fmaf(S[4 * m + 2], qv.z, o2);
+                S[4 * m + 3] = fmaf(kr[m].w, u, S[4 * m + 3]); o3 = fmaf(S[4 * m + 3], qv.w, o3);
             }
-            float o = o0 + o1;
+            float o = (o0 + o1) + (o2 + o3);
             for (int off = CW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
             if (r == 0 && col_ok) p.out[size_t(t0 + c0 + tt) * p.ldo + size_t(h) * Dv + j] = o;
         }
+        __syncthreads();                                   // this buffer is loaded again two chunks on
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
     for (int m = 0; m < NR; ++m) {
-        const int i = r + R * m;
+        const int i = r * NR + m;
         if (i < D && col_ok) sp[size_t(i) * Dv + j] = S[m];
     }
 }
@@ -219,30 +276,47 @@ static void delta_rule_shape(int D, int* nr, int* r) {
     *r = R;
 }
 
+// Floats of scratch for the prepared rows of T tokens: qk, gb and vf one after the other.
+GB_API long long gb_delta_rule_scratch_floats(int T, int H, int G, int D, int Dv) {
+    const long long DA = (D + 3) / 4 * 4, VA = (Dv + 3) / 4 * 4;
+    return (long long)T * (G * 2 * DA + H * (DA + 4) + H * VA);
+}
+
 GB_API int gb_delta_rule(const void* q, const void* k, const void* v, int dtype, long long ld, const void* beta,
                          long long ld_beta, const void* a, long long ld_a, const void* dt_bias, const void* A_log,
                          int w_dtype, float* state, float* out, long long ldo, const int* cu, const int* slots,
-                         const int* qlens, int B, int H, int G, int D, int Dv, float q_scale, cudaStream_t stream) {
+                         const int* qlens, int T, int B, int H, int G, int D, int Dv, float q_scale, float* scratch,
+                         cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(w_dtype), "gb_delta_rule: bad dtype");
     GB_REQUIRE(H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0, "gb_delta_rule: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d", H, G, D, Dv);
     GB_REQUIRE(D <= 2048, "gb_delta_rule: key size %d exceeds 2048", D);
-    GB_REQUIRE(H <= 65535, "gb_delta_rule: too many heads (%d)", H);
-    if (B == 0) return 0;
+    GB_REQUIRE(H + G <= 4 * 65535, "gb_delta_rule: too many heads (%d)", H);
+    GB_REQUIRE(scratch && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0, "gb_delta_rule: scratch missing or misaligned");
+    if (B == 0 || T == 0) return 0;
+    const int DA = (D + 3) / 4 * 4, VA = (Dv + 3) / 4 * 4;
+    DeltaPrepParams pp;
+    pp.q = q; pp.k = k; pp.v = v; pp.beta = beta; pp.a = a; pp.dt_bias = dt_bias; pp.A_log = A_log;
+    pp.qk = scratch;
+    pp.gb = pp.qk + size_t(T) * G * 2 * DA;
+    pp.vf = pp.gb + size_t(T) * H * (DA + 4);
+    pp.ld = ld; pp.ld_beta = ld_beta; pp.ld_a = ld_a; pp.dtype = dtype; pp.w_dtype = w_dtype;
+    pp.H = H; pp.G = G; pp.D = D; pp.Dv = Dv; pp.DA = DA; pp.VA = VA; pp.q_scale = q_scale;
+    delta_prep_kernel<<<dim3(T, (H + G + 3) / 4), 128, 0, stream>>>(pp);
+    GB_LAUNCH_OK("gb_delta_rule (prepare)");
     DeltaRuleParams p;
-    p.q = q; p.k = k; p.v = v; p.beta = beta; p.a = a; p.dt_bias = dt_bias; p.A_log = A_log; p.state = state; p.out = out;
-    p.cu = cu; p.slots = slots; p.qlens = qlens; p.ld = ld; p.ld_beta = ld_beta; p.ld_a = ld_a; p.ldo = ldo;
-    p.dtype = dtype; p.w_dtype = w_dtype; p.H = H; p.G = G; p.D = D; p.Dv = Dv; p.q_scale = q_scale;
+    p.qk = pp.qk; p.gb = pp.gb; p.vf = pp.vf; p.state = state; p.out = out; p.cu = cu; p.slots = slots; p.qlens = qlens;
+    p.ldo = ldo; p.H = H; p.G = G; p.D = D; p.Dv = Dv; p.DA = DA; p.VA = VA;
     int NR, R;
     delta_rule_shape(D, &NR, &R);
-    const int CB = 4 * (32 / R), DP = R * NR;
-    const int per_token = 4 * (3 * DP + CB + 1);
-    int TC = (40 * 1024) / per_token;
+    const int CB = 4 * (32 / R);
+    const int per_token = 4 * (3 * R * (NR + 4) + 4 + CB);
+    int TC = (20 * 1024) / per_token;                    // two buffers of at most 20 KB each
     TC = TC < 1 ? 1 : (TC > 16 ? 16 : TC);
     p.R = R; p.TC = TC;
-    const size_t smem = size_t(TC) * per_token;
+    const size_t smem = size_t(2) * TC * per_token;
     GB_REQUIRE(smem <= 48 * 1024, "gb_delta_rule: key size %d needs %zu bytes of shared memory", D, smem);
     dim3 grid(B, H, (Dv + CB - 1) / CB);
-    GB_REQUIRE(grid.z <= 65535, "gb_delta_rule: value size %d is too large", Dv);
+    GB_REQUIRE(grid.z <= 65535 && H <= 65535, "gb_delta_rule: too many heads or value columns");
     if (NR == 32) delta_rule_kernel<32><<<grid, 128, smem, stream>>>(p);
     else delta_rule_kernel<64><<<grid, 128, smem, stream>>>(p);
     GB_LAUNCH_OK("gb_delta_rule");

@@ -155,7 +155,8 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
     """The gated delta rule with a decay per head and key channel over this step's tokens, from and into
     state [slots, heads, dim, vdim] (float32).  q, k [T, kv_heads*dim] and v [T, heads*vdim] are column slices
     of one buffer (after convolution and SiLU); beta [T, heads] and a [T, heads*dim] are the projections'
-    outputs before sigmoid and softplus; out float32 [T, heads*vdim] is what the state gives for q."""
+    outputs before sigmoid and softplus; out float32 [T, heads*vdim] is what the state gives for q.
+    Two launches: what does not depend on the state for all tokens at once (into a workspace buffer), then the walk."""
     _cuda(q, k, v, beta, a, dt_bias, a_log, state, out)
     T = q.shape[0]
     ld = q.stride(0)
@@ -164,9 +165,11 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
     assert state.dtype == torch.float32 and state.shape[1:] == (n_heads, dim, vdim) and state.is_contiguous()
     assert out.dtype == torch.float32 and out.shape == (T, n_heads * vdim) and out.stride(1) == 1
     assert dt_bias.dtype == a_log.dtype and dt_bias.numel() == n_heads * dim and a_log.numel() == n_heads
+    need = native.library().gb_delta_rule_scratch_floats(T, n_heads, n_kv_heads, dim, vdim)
+    scratch = ctx.ws.get("delta.prepared", (need,), torch.float32)
     call("gb_delta_rule", ptr(q), ptr(k), ptr(v), dtype_code(q), ld, ptr(beta), beta.stride(0), ptr(a), a.stride(0),
          ptr(dt_bias), ptr(a_log), dtype_code(dt_bias), ptr(state), ptr(out), out.stride(0), ptr(ctx.cu), ptr(ctx.slots),
-         ptr(ctx.qlens), ctx.B, n_heads, n_kv_heads, dim, vdim, float(q_scale), stream_ptr())
+         ptr(ctx.qlens), T, ctx.B, n_heads, n_kv_heads, dim, vdim, float(q_scale), ptr(scratch), stream_ptr())
     return out
 
 
@@ -395,6 +398,20 @@ def decode_split_class(max_kv: int) -> int:
 def decode_split_class_cuda(max_kv: int) -> int:
     """The same for the CUDA-core decode kernel, whose splits (decode_splits with mma False) follow an eighth of the pages."""
     return _split_class(((max_kv + 63) // 64) // 8)
+
+
+def decode_split_class_exact(max_kv: int) -> int:
+    """Class of a decode step of the normalised attention on the CUDA-core decode kernel: half of the pages."""
+    return _split_class(((max_kv + 63) // 64) // 2)
+
+
+def decode_splits_exact(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int) -> int:
+    """Splits of each sequence's pages for that kernel: two pages or more per split while all CTAs fit the device at
+    once with two per SM (the rule of decode_splits leaves a step of 8 sequences of 512 positions at 32 CTAs)."""
+    group = n_heads // n_kv_heads
+    tile = 8 if group >= 8 else 4 if group > 2 else group
+    ctas = T * n_kv_heads * ((group + tile - 1) // tile)
+    return max(1, min(decode_split_class_exact(max_kv), 32, (2 * sms) // ctas))
 
 
 def decode_splits(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int, mma: bool) -> int:

@@ -117,7 +117,8 @@ class Attention(Part):
         if self.exact:
             # the general kernel: one block per token and head, whatever the lengths; the CUDA-core decode kernel
             # splits each sequence's pages by a rule of the longest sequence
-            return ("cuda", kernels.decode_split_class_cuda(batch.max_kv)) if self._exact_decode() else ()
+            max_kv = min(batch.max_kv, self.window) if self.window else batch.max_kv
+            return ("cuda", kernels.decode_split_class_exact(max_kv)) if self._exact_decode() else ()
         return kernels.decode_split_class(min(batch.max_kv, self.window) if self.window else batch.max_kv)
 
     def absorb_input_norm(self, weight: torch.Tensor) -> bool:
@@ -170,9 +171,10 @@ class Attention(Part):
             kernels.attention_prefill(q, out, nh, nkv, hd, tiles, ctx.cu, ctx.starts, ctx.qlens, table, run.ring_pages,
                                       run.k, run.v, self.window or 0, self.scale, tc=False, exact=True)
         elif ctx.decode and self._exact_decode() and kernels.attention_decode_supported(q, run.k, hd):
+            max_kv = min(ctx.max_kv, self.window) if self.window else ctx.max_kv
+            splits = kernels.decode_splits_exact(q.shape[0], nh, nkv, max_kv, kernels.tc_scratch(q.device).sms)
             kernels.attention_decode(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
-                                     self.window or 0, self.scale, mma=False,
-                                     max_kv=min(ctx.max_kv, self.window) if self.window else ctx.max_kv)
+                                     self.window or 0, self.scale, mma=False, max_kv=max_kv, splits=splits)
         else:
             kernels.attention_generic(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
                                       self.window or 0, self.scale, v_dim=vd)

@@ -19,7 +19,7 @@ def assert_close(got, want, dtype, what=""):
     """32-bit: the largest error against the largest value of the compared block, 1e-4 (the sharp test: a key left
     out, a state not carried or a wrong edge moves results by far more).  bfloat16: rounding of the intermediates
     moves single values of these small, peaked models by a few percent, so the root mean square of the error is held
-    to 2.5% of the block's and the largest error to 6% of the largest value."""
+    to 5% of the block's and the largest error to 10% of the largest value."""
     got, want = got.detach().float().cpu(), want.detach().float().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} != {tuple(want.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite values"
@@ -28,7 +28,7 @@ def assert_close(got, want, dtype, what=""):
         assert err <= TOL[dtype] * ref, f"{what}: max error {err:.3e} against max |ref| {ref:.3e} ({dtype})"
         return
     rms_err, rms_ref = float((got - want).pow(2).mean().sqrt()), max(float(want.pow(2).mean().sqrt()), 1e-6)
-    assert rms_err <= 2.5e-2 * rms_ref and err <= 6e-2 * ref, \
+    assert rms_err <= 5e-2 * rms_ref and err <= 1e-1 * ref, \
         f"{what}: rms error {rms_err:.3e} of {rms_ref:.3e}, max error {err:.3e} of {ref:.3e} ({dtype})"
 DEV = "cuda:0"
 DTYPES = ["float32", "bfloat16"]
