@@ -54,6 +54,20 @@ def causal_conv_silu(x, taps):
     return silu(out)
 
 
+def delta_recurrence(q, k, v, beta, decay, S=None):
+    """One head.  q, k [n, D] (unit vectors, q already scaled), v [n, Dv], beta [n], decay [n, D]; S [D, Dv] or None
+    (zeros).  Per token: S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.  Returns (out, S)."""
+    n, D = q.shape
+    S = torch.zeros(D, v.shape[1], dtype=q.dtype) if S is None else S.clone()
+    out = torch.zeros(n, v.shape[1], dtype=q.dtype)
+    for t in range(n):
+        S = decay[t][:, None] * S
+        u = beta[t] * (v[t] - S.T @ k[t])
+        S = S + torch.outer(k[t], u)
+        out[t] = S.T @ q[t]
+    return out, S
+
+
 def channel_delta(h, w, p, m, eps):
     """The gated delta rule with one decay per head and key channel.  m: the layer's mixer sizes."""
     n = h.shape[0]
@@ -71,12 +85,7 @@ def channel_delta(h, w, p, m, eps):
     out = torch.zeros(n, H, Dv, dtype=h.dtype)
     for hd in range(H):
         g = hd // (H // G)
-        S = torch.zeros(D, Dv, dtype=h.dtype)
-        for t in range(n):
-            S = decay[t, hd][:, None] * S
-            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
-            S = S + torch.outer(k[t, g], u)
-            out[t, hd] = S.T @ q[t, g]
+        out[:, hd], _ = delta_recurrence(q[:, g], k[:, g], v[:, hd], beta[:, hd], decay[:, hd])
     out = rms_unit(out, eps) * w[p + "norm"].to(h.dtype) * gate
     return lin(out.reshape(n, H * Dv), w[p + "o"])
 

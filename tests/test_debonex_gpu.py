@@ -126,6 +126,46 @@ def test_short_convolution_carries_its_inputs_over_cuts(taps):
         assert torch.allclose(torch.cat(got[b]), P.causal_conv_silu(x[b], w), atol=1e-5)
 
 
+@pytest.mark.parametrize("D,Dv,H,G", [(8, 5, 2, 1), (24, 40, 4, 2), (300, 36, 2, 2), (600, 20, 1, 1), (1100, 12, 1, 1)])
+def test_delta_rule_kernel_at_every_shape_of_its_walk(D, Dv, H, G):
+    """The recurrence alone in 32-bit, at key sizes that take 8, 16, 32 and 64 rows a lane, sizes that are no multiple
+    of four, fewer q/k heads than heads; two sequences in a step, then both continued from their states."""
+    from gguf_rs_cli_b200 import kernels
+    eng = new_engine("small", "float32")
+    g = torch.Generator().manual_seed(D)
+    lens = [[9, 4], [1, 3]]
+    n = [sum(x) for x in zip(*lens)]
+    raw = {b: dict(q=torch.randn(n[b], G * D, generator=g), k=torch.randn(n[b], G * D, generator=g),
+                   v=torch.randn(n[b], H * Dv, generator=g), beta=torch.randn(n[b], H, generator=g),
+                   a=torch.randn(n[b], H * D, generator=g) * 2) for b in range(2)}
+    dt_bias, a_log = torch.rand(H * D, generator=g) * 4 - 5, torch.rand(H, generator=g) * 2 - 1.5
+    want = []
+    for b in range(2):
+        r = raw[b]
+        q, k = r["q"].reshape(-1, G, D), r["k"].reshape(-1, G, D)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        decay = torch.exp(-torch.exp(a_log)[None, :, None] * P.softplus(r["a"] + dt_bias).reshape(-1, H, D))
+        beta = torch.sigmoid(r["beta"])
+        want.append(torch.stack([P.delta_recurrence(q[:, h // (H // G)], k[:, h // (H // G)], r["v"].reshape(-1, H, Dv)[:, h],
+                                                    beta[:, h], decay[:, h])[0] for h in range(H)], dim=1).reshape(-1, H * Dv))
+    state = torch.zeros(eng.cache.n_slots, H, D, Dv, device=DEV)
+    slots, fed, got = [eng.open(), eng.open()], [0, 0], [[], []]
+    for cut in lens:
+        ctx, _, _ = eng.plan([entry(s, [1] * c, ()) for s, c in zip(slots, cut)])
+        rows = {name: torch.cat([raw[b][name][fed[b]:fed[b] + cut[b]] for b in range(2)]).to(DEV) for name in ("q", "k", "v", "beta", "a")}
+        qkv = torch.cat([rows["q"], rows["k"], rows["v"]], dim=1).contiguous()
+        out = torch.empty(sum(cut), H * Dv, device=DEV)
+        kernels.delta_rule(qkv[:, :G * D], qkv[:, G * D:2 * G * D], qkv[:, 2 * G * D:], rows["beta"], rows["a"], dt_bias.to(DEV),
+                           a_log.to(DEV), state, out, ctx, H, G, D, Dv, D ** -0.5)
+        eng.cache.advance(slots, cut)
+        got[0].append(out[:cut[0]].cpu())
+        got[1].append(out[cut[0]:].cpu())
+        fed = [fed[0] + cut[0], fed[1] + cut[1]]
+    for b in range(2):
+        assert_close(torch.cat(got[b]), want[b], "float32", f"delta rule D={D} sequence {b}")
+
+
 # ------------------------------------------------------------ whole models
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
