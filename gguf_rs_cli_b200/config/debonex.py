@@ -36,6 +36,13 @@ def _get(raw: Dict[str, Any], key: str, where: str, kind=int, positive: bool = T
     return v
 
 
+def _factor(raw, key: str, where: str) -> float:
+    """A constant factor; a configuration that does not name it has none (1)."""
+    if not isinstance(raw, dict) or raw.get(key) is None:
+        return 1.0
+    return _get(raw, key, where, float, positive=False)
+
+
 MIXER_TYPES = ("channel_delta", "latent_attention", "attention")
 
 
@@ -68,8 +75,8 @@ class DebonexConfig:
                 raise ConfigError(f"config.json: {where}.type {kind!r} is not one of {list(MIXER_TYPES)}")
             out.append(DebonexLayer(kind, _read_mixer(kind, entry.get("mixer"), where + ".mixer"), _read_mlp(entry.get("mlp"), where + ".mlp")))
         return cls(vocab=_get(raw, "vocab", "the top level"), width=_get(raw, "width", "the top level"),
-                   embedding_scale=_get(raw.get("embedding"), "scale", "'embedding'", float, positive=False),
-                   logit_scale=_get(raw, "logit_scale", "the top level", float, positive=False),
+                   embedding_scale=_factor(raw.get("embedding"), "scale", "'embedding'"),
+                   logit_scale=_factor(raw, "logit_scale", "the top level"),
                    norm_eps=_get(raw.get("norm"), "eps", "'norm'", float), layers=out)
 
 

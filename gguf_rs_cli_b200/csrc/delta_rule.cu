@@ -39,6 +39,58 @@ __global__ void short_conv_silu_kernel(const void* __restrict__ xin, int dtype, 
     }
 }
 
+// The same for bfloat16 rows that start on 16 bytes: a thread takes 8 neighbouring channels with 16-byte loads
+// and stores; taps_t [K, C] holds the taps tap by tap.  The products are added in the same order as above.
+__device__ __forceinline__ void conv_unpack8(uint4 raw, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 v = __bfloat1622float2(h[e]);
+        f[2 * e] = v.x;
+        f[2 * e + 1] = v.y;
+    }
+}
+
+__global__ void __launch_bounds__(128) short_conv_silu_vec_kernel(
+        const __nv_bfloat16* __restrict__ xin, long long ldx, int C, int K, const __nv_bfloat16* __restrict__ taps_t,
+        const float* __restrict__ state, const int* __restrict__ seq_of, const int* __restrict__ cu,
+        const int* __restrict__ slots, __nv_bfloat16* __restrict__ out, long long ldo) {
+    const int t = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= C) return;
+    const int b = seq_of[t];
+    uint4* dst = reinterpret_cast<uint4*>(out + size_t(t) * ldo + c);
+    if (b < 0) {
+        *dst = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const int first = cu[b], i = t - first, slot = slots[b];
+    const float* st = state + size_t(slot) * (K - 1) * C;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int src = i - (K - 1 - j);
+        float xv[8], tw[8];
+        if (src >= 0) {
+            conv_unpack8(*reinterpret_cast<const uint4*>(xin + size_t(first + src) * ldx + c), xv);
+        } else {
+            const float4* sp = reinterpret_cast<const float4*>(st + size_t(K - 1 + src) * C + c);
+            const float4 lo = sp[0], hi = sp[1];
+            xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w; xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
+        }
+        conv_unpack8(*reinterpret_cast<const uint4*>(taps_t + size_t(j) * C + c), tw);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(xv[e], tw[e], acc[e]);
+    }
+    uint4 packed;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+        o2[e] = __floats2bfloat162_rn(acc[2 * e] / (1.f + expf(-acc[2 * e])), acc[2 * e + 1] / (1.f + expf(-acc[2 * e + 1])));
+    *dst = packed;
+}
+
 // After the convolution: the sequence's carried inputs become the last K-1 inputs including this step's.
 // blockIdx.x is the sequence, blockIdx.y a slice of channels; a thread owns a channel, reads all it needs and
 // then writes.
@@ -70,9 +122,10 @@ __global__ void short_conv_carry_kernel(const void* __restrict__ xin, int dtype,
 
 // xin: [T, C] with pitch ldx (the projections' outputs); taps [C, K], last column on the current token;
 // state f32 [slots, K-1, C]; out [T, C] with pitch ldo, same dtype as xin.  The carried inputs are renewed.
+// taps_t (optional): the taps again as bfloat16 [K, C], for the kernel of 16-byte accesses.
 GB_API int gb_short_conv_silu(const void* xin, int dtype, long long ldx, int T, int B, int C, int K, const void* taps,
-                              int taps_dtype, float* state, const int* seq_of, const int* cu, const int* slots,
-                              const int* qlens, void* out, long long ldo, cudaStream_t stream) {
+                              int taps_dtype, const void* taps_t, float* state, const int* seq_of, const int* cu,
+                              const int* slots, const int* qlens, void* out, long long ldo, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(taps_dtype), "gb_short_conv_silu: bad dtype");
     GB_REQUIRE(C > 0 && K >= 1 && K <= CONV_MAX_TAPS && ldx >= C && ldo >= C, "gb_short_conv_silu: bad sizes C=%d taps=%d (1..%d)",
                C, K, CONV_MAX_TAPS);
@@ -80,7 +133,14 @@ GB_API int gb_short_conv_silu(const void* xin, int dtype, long long ldx, int T, 
     if (T == 0) return 0;
     const int threads = 128, slices = (C + threads - 1) / threads;
     GB_REQUIRE(slices <= 65535, "gb_short_conv_silu: too many channels (%d)", C);
-    short_conv_silu_kernel<<<dim3(T, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, taps, taps_dtype, state, seq_of, cu, slots, out, ldo);
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    if (taps_t && dtype == GB_BF16 && C % 8 == 0 && ldx % 8 == 0 && ldo % 8 == 0 && aligned16(xin) && aligned16(out) &&
+        aligned16(taps_t) && (K == 1 || (reinterpret_cast<uintptr_t>(state) & 31) == 0)) {
+        short_conv_silu_vec_kernel<<<dim3(T, (C / 8 + threads - 1) / threads), threads, 0, stream>>>(
+            (const __nv_bfloat16*)xin, ldx, C, K, (const __nv_bfloat16*)taps_t, state, seq_of, cu, slots, (__nv_bfloat16*)out, ldo);
+    } else {
+        short_conv_silu_kernel<<<dim3(T, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, taps, taps_dtype, state, seq_of, cu, slots, out, ldo);
+    }
     GB_LAUNCH_OK("gb_short_conv_silu");
     if (K > 1 && B > 0) {
         short_conv_carry_kernel<<<dim3(B, slices), threads, 0, stream>>>(xin, dtype, ldx, C, K, state, cu, slots, qlens);

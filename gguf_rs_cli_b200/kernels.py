@@ -134,18 +134,21 @@ def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
     return x
 
 
-def short_conv_silu(xin: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], ctx, out: torch.Tensor) -> torch.Tensor:
+def short_conv_silu(xin: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], ctx, out: torch.Tensor,
+                    taps_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, c] = silu(sum_j taps[c, j] * xin[t - (K-1-j), c]) per sequence; rows before the step come from
     state [slots, K-1, C] (float32), which is then renewed with the sequence's last K-1 inputs.
-    xin, out: [T, C] column slices (unit stride along c)."""
-    _cuda(xin, taps, state, out)
+    xin, out: [T, C] column slices (unit stride along c).  taps_t: the taps once more as bfloat16 [K, C]; with it,
+    bfloat16 rows that start on 16 bytes are read and written 8 channels at a time."""
+    _cuda(xin, taps, state, out, taps_t)
+    assert taps_t is None or (taps_t.dtype == torch.bfloat16 and taps_t.shape == (taps.shape[1], taps.shape[0]) and taps_t.is_contiguous())
     T, C = xin.shape
     K = taps.shape[1]
     assert taps.shape == (C, K) and taps.is_contiguous() and xin.stride(1) == 1 and out.stride(1) == 1
     assert out.shape == (T, C) and out.dtype == xin.dtype
     assert state is None or (state.dtype == torch.float32 and state.shape[1:] == (K - 1, C) and state.is_contiguous())
     call("gb_short_conv_silu", ptr(xin), dtype_code(xin), xin.stride(0), T, ctx.B, C, K, ptr(taps), dtype_code(taps),
-         ptr(state), ptr(ctx.seq_of), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(out), out.stride(0), stream_ptr())
+         ptr(taps_t), ptr(state), ptr(ctx.seq_of), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens), ptr(out), out.stride(0), stream_ptr())
     return out
 
 

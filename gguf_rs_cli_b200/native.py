@@ -143,7 +143,7 @@ _SIGNATURES = {
     "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _P],
     "gb_add_dyt": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P],
     "gb_scale": [_P, _L, _F, _P],
-    "gb_short_conv_silu": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _L, _P],
+    "gb_short_conv_silu": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _L, _P],
     "gb_delta_rule": [_P, _P, _P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "gb_delta_rule_scratch_floats": [_I, _I, _I, _I, _I],
     "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _P],

@@ -97,6 +97,7 @@ class ChannelDeltaRule(Part):
             parts.append(torch.zeros(pad, parts[0].shape[1], dtype=dt, device=parts[0].device))
         self.proj = Linear(torch.cat(parts, dim=0).contiguous(), name="delta.proj")
         self.taps = torch.cat([w["q_conv"], w["k_conv"], w["v_conv"]], dim=0).to(dt).contiguous()
+        self.taps_t = self.taps.t().contiguous() if dt == torch.bfloat16 else None      # tap by tap, for 16-byte loads
         self.a2 = Linear(w["a2"], name="delta.a")
         self.g2 = Linear(w["g2"], name="delta.gate")
         self.dt_bias, self.a_log = w["dt_bias"].to(dt).contiguous(), w["A_log"].to(dt).contiguous()
@@ -113,7 +114,7 @@ class ChannelDeltaRule(Part):
         ctx.mark("projections")
         conv = ctx.ws.get("delta.conv", (T, C), ctx.dtype)
         carried = ctx.state(f"run{run.index}.conv") if self.K > 1 else None
-        kernels.short_conv_silu(proj[:, :C], self.taps, carried, ctx, conv)
+        kernels.short_conv_silu(proj[:, :C], self.taps, carried, ctx, conv, taps_t=self.taps_t)
         a = self.a2(proj[:, self.off["a1"]:self.off["a1"] + self.ra], ctx)
         gate = self.g2(proj[:, self.off["g1"]:self.off["g1"] + self.rg], ctx)
         ctx.mark("conv_gates")

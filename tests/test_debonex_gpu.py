@@ -98,17 +98,21 @@ def test_each_mixer_alone_in_an_unequal_batch(name, dtype):
         assert_close(got, torch.cat(want), dtype, f"{name} layer {i} ({layer['type']})")
 
 
+@pytest.mark.parametrize("wide", [False, True])
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
-def test_short_convolution_carries_its_inputs_over_cuts(taps):
+def test_short_convolution_carries_its_inputs_over_cuts(taps, wide):
     """The convolution kernel alone: a sequence fed in pieces of 1, 2, 3 and more rows gives what it gives whole,
-    beside a second sequence in the same step."""
+    beside a second sequence in the same step.  wide: bfloat16 rows of 40 channels, which the kernel of 16-byte
+    accesses takes; else 32-bit rows of 37."""
     from gguf_rs_cli_b200 import kernels
     from gguf_rs_cli_b200.engine.step import Engine
     eng = new_engine("small", "float32")
     g = torch.Generator().manual_seed(taps)
-    C, n = 37, 23
+    C, n = (40, 23) if wide else (37, 23)
     x = torch.randn(2, n, C, generator=g)
     w = torch.randn(C, taps, generator=g)
+    if wide:
+        x, w = x.to(torch.bfloat16), w.to(torch.bfloat16)
     state = torch.zeros(eng.cache.n_slots, max(taps - 1, 1), C, device=DEV) if taps > 1 else None
     slots = [eng.open(), eng.open()]
     fed, got = [0, 0], [[], []]
@@ -116,14 +120,15 @@ def test_short_convolution_carries_its_inputs_over_cuts(taps):
         ctx, _, _ = eng.plan([entry(slots[0], [1] * cut_a, ()), entry(slots[1], [1] * cut_b, ())])
         rows = torch.cat([x[0, fed[0]:fed[0] + cut_a], x[1, fed[1]:fed[1] + cut_b]]).to(DEV)
         out = torch.empty_like(rows)
-        kernels.short_conv_silu(rows, w.to(DEV), state, ctx, out)
+        kernels.short_conv_silu(rows, w.to(DEV), state, ctx, out, taps_t=w.t().contiguous().to(DEV) if wide else None)
         eng.cache.advance(slots, [cut_a, cut_b])
-        got[0].append(out[:cut_a].cpu())
-        got[1].append(out[cut_a:].cpu())
+        got[0].append(out[:cut_a].float().cpu())
+        got[1].append(out[cut_a:].float().cpu())
         fed = [fed[0] + cut_a, fed[1] + cut_b]
     assert fed == [n, n]
     for b in range(2):
-        assert torch.allclose(torch.cat(got[b]), P.causal_conv_silu(x[b], w), atol=1e-5)
+        want = P.causal_conv_silu(x[b].float(), w.float())
+        assert torch.allclose(torch.cat(got[b]), want, atol=2e-2 * float(want.abs().max()) if wide else 1e-5)
 
 
 @pytest.mark.parametrize("D,Dv,H,G", [(8, 5, 2, 1), (24, 40, 4, 2), (300, 36, 2, 2), (600, 20, 1, 1), (1100, 12, 1, 1)])
@@ -314,6 +319,40 @@ def test_a_far_key_that_stands_out_in_prompt_and_decode(far, dtype):
     got = model.layers[0].mixer.forward(hd[n - 1:], ctx, eng.runs[0])
     assert_close(got, want[n - 1:], dtype, f"far key {far} seen from a decoded token")
     eng.close(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,heads,kv_heads", [(48, 4, 2), (80, 2, 2), (128, 8, 1), (256, 2, 1)])
+def test_attention_layer_with_keys_and_values_of_one_size(hd, heads, kv_heads, dtype):
+    """The normalised attention alone where keys and values have one size: in bfloat16 single tokens then take the
+    CUDA-core decode kernel (any multiple of 16 up to 256) and prompts of 128 the tiled one; 140 rows as a prompt,
+    then 70 more one by one over the page border at 192, with page splits in the longer of two sequences."""
+    from gguf_rs_cli_b200.engine.step import Engine
+    cfg = config("small")
+    cfg["layers"] = [cfg["layers"][0]]
+    cfg["layers"][0]["mixer"].update(heads=heads, kv_heads=kv_heads, dim=hd, vdim=hd, scale=2.0 / hd ** 0.5,
+                                     q_temp={"coef": 0.4, "every": 64})
+    w = make_weights(cfg, {}, seed=hd)
+    m, eps = cfg["layers"][0]["mixer"], cfg["norm"]["eps"]
+    model = build(cfg, w, dtype).model
+    eng = Engine(model, n_tokens=2048, n_slots=2)
+    g = torch.Generator().manual_seed(hd)
+    n, n0 = 210, 140
+    h = torch.randn(n, cfg["width"], generator=g).to(torch.bfloat16).float()
+    want = P.normed_attention(h, w, "l0.mix.", m, eps)
+    hd_ = h.to(tdtype(dtype)).to(DEV)
+    a, b = eng.open(), eng.open()
+    ctx, _, _ = eng.plan([entry(a, [1] * n0, ()), entry(b, [1] * 3, ())])
+    got = model.layers[0].mixer.forward(torch.cat([hd_[:n0], hd_[:3]]), ctx, eng.runs[0])
+    assert_close(got[:n0], want[:n0], dtype, f"prompt, heads of {hd}")
+    assert_close(got[n0:], want[:3], dtype, f"short prompt beside it, heads of {hd}")
+    eng.cache.advance([a, b], [n0, 3])
+    for t in range(n0, n):
+        ctx, _, _ = eng.plan([entry(a, [1], ()), entry(b, [1], ())])
+        got = model.layers[0].mixer.forward(torch.stack([hd_[t], hd_[3 + t - n0]]), ctx, eng.runs[0])
+        eng.cache.advance([a, b], [1, 1])
+        assert_close(got[:1], want[t:t + 1], dtype, f"row {t} alone, heads of {hd}")
+        assert_close(got[1:], want[3 + t - n0:4 + t - n0], dtype, f"row {3 + t - n0} of the short sequence, heads of {hd}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -27,6 +27,17 @@ def test_config_reads_every_size_and_constant():
     assert spec.layers[0].feed_forward.params["activation"] == "gelu_tanh"
 
 
+def test_config_without_factors_has_none():
+    from gguf_rs_cli_b200.config import load_config
+    raw = config("small")
+    del raw["embedding"], raw["logit_scale"]
+    raw["layers"][0]["mixer"].pop("q_temp")
+    raw["layers"][3].pop("mlp")
+    _, cfg = load_config(raw)
+    assert (cfg.embedding_scale, cfg.logit_scale) == (1.0, 1.0)
+    assert cfg.layers[0].mixer["q_temp"] is None and cfg.layers[3].ff is None
+
+
 @pytest.mark.parametrize("path,value,match", [
     (("layers", 0, "type"), "conv_mixer", "not one of"),
     (("layers", 1, "mixer", "kv_heads"), 3, "not a multiple"),
