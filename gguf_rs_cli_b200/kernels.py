@@ -244,6 +244,34 @@ def pack_latent_heads(kv: torch.Tensor, row: torch.Tensor, n_heads: int, dim: in
          ptr(table), table.shape[1], ptr(k_pages), ptr(v_pages), stream_ptr())
 
 
+def latent_decode_supported(n_heads: int, kv_rank: int, rot_dim: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and bool(native.library().gb_latent_decode_supported(n_heads, kv_rank, rot_dim, 1, 1))
+
+
+def latent_decode_class(max_kv: int) -> int:
+    """Class of a decode step for the latent decode kernel: half of the longest sequence's blocks of 32 keys, rounded
+    down to one of a few values; steps of one class split their keys alike."""
+    return _split_class(((max_kv + 31) // 32) // 2)
+
+
+def latent_decode(qa: torch.Tensor, out: torch.Tensor, n_heads: int, kv_rank: int, rot_dim: int, ctx, table: torch.Tensor,
+                  ring_pages: int, cache: torch.Tensor, scale: float) -> torch.Tensor:
+    """Latent attention of single tokens: qa [T, heads*(kv_rank + rot_dim)] (queries in the latent's space, then the
+    rotated part), cache rows [kv_rank + rot_dim]; out [T, heads*kv_rank] is the mix of the rows' first kv_rank
+    entries.  One pass over each token's rows serves all heads; the rows are split over CTAs (two blocks of 32 keys or
+    more per split, while two CTAs per SM hold the step) and merged in order."""
+    _cuda(qa, out, table, cache)
+    T = qa.shape[0]
+    assert qa.dtype == out.dtype == cache.dtype == torch.bfloat16 and qa.stride(1) == 1 and out.stride(1) == 1
+    assert qa.shape[1] == n_heads * (kv_rank + rot_dim) and out.shape == (T, n_heads * kv_rank) and cache.shape[-1] == kv_rank + rot_dim
+    lib = native.library()
+    splits = max(1, min(latent_decode_class(ctx.max_kv), 64, (2 * tc_scratch(qa.device).sms) // max(T, 1)))
+    scratch = ctx.ws.get("latent.partial", (lib.gb_latent_decode_scratch_floats(T, n_heads, kv_rank, splits),), torch.float32)
+    call("gb_latent_decode", ptr(qa), qa.stride(0), ptr(out), out.stride(0), T, n_heads, kv_rank, rot_dim, ptr(ctx.seq_of),
+         ptr(ctx.pos), ptr(table), table.shape[1], ring_pages, ptr(cache), float(scale), splits, ptr(scratch), stream_ptr())
+    return out
+
+
 def head_matmul(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int) -> torch.Tensor:
     """out[t, h*out_head_stride + o] = sum_i x[t, h*x_head_stride + i] * w[h, i, o]; w [heads, in, out]."""
     _cuda(x, w, out)

@@ -150,6 +150,9 @@ _SIGNATURES = {
     "gb_qk_norm_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P],
     "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _P],
     "gb_pack_latent_heads": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
+    "gb_latent_decode_supported": [_I, _I, _I, _I, _I],
+    "gb_latent_decode_scratch_floats": [_I, _I, _I, _I],
+    "gb_latent_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P],
     "gb_head_matmul": [_P, _I, _L, _I, _P, _I, _I, _I, _I, _P, _I, _L, _I, _I, _P],
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
     "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P],
@@ -182,7 +185,7 @@ _SIGNATURES = {
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }
-_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
+_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:
@@ -218,7 +221,7 @@ def library():
 
 _launches = 0
 # kernels launched by one call of an entry point, where that is not one
-KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2}
+KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2}
 
 
 def launch_count() -> int:

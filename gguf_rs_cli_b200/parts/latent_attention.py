@@ -99,7 +99,15 @@ class LatentAttention(Part):
         return {"tiles": kernels.attention_prefill_tiles(batch.qlens), "pages": table, "n_pages": [base]}
 
     accepts_residual = True
-    graph_class = ()              # one block per token and head, whatever the lengths
+
+    def _fast_decode(self) -> bool:
+        """Whether single tokens take the kernel that serves all heads from one pass over the latent rows."""
+        return kernels.latent_decode_supported(self.H, self.C, self.R, self.dtype)
+
+    def graph_class(self, batch: HostBatch):
+        """The decode kernel splits each token's keys by a rule of the longest sequence; the general kernel launches one
+        block per token and head whatever the lengths."""
+        return ("latent", kernels.latent_decode_class(batch.max_kv)) if self._fast_decode() else ()
 
     def forward(self, h, ctx: StepContext, run: RunView, residual=None) -> Optional[torch.Tensor]:
         H, D, R, Dv, C = self.H, self.D, self.R, self.Dv, self.C
@@ -134,8 +142,11 @@ class LatentAttention(Part):
                             self.norm_weight, self.p["eps"], qa, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k)
         kernels.head_matmul(q, D + R, self.uk, qa, C + R)
         mix = ctx.ws.get("latent.mix", (T, H * C), ctx.dtype)
-        kernels.attention_generic(qa, mix, H, 1, C + R, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, None, 0,
-                                  float(self.p["scale"]), v_dim=C)
+        if ctx.decode and self._fast_decode():
+            kernels.latent_decode(qa, mix, H, C, R, ctx, table, run.ring_pages, run.k, float(self.p["scale"]))
+        else:
+            kernels.attention_generic(qa, mix, H, 1, C + R, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, None, 0,
+                                      float(self.p["scale"]), v_dim=C)
         ctx.mark("attention")
         values = ctx.ws.get("latent.values", (T, H * Dv), ctx.dtype)
         kernels.head_matmul(mix, C, self.uv_t, values, Dv)

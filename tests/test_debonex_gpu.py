@@ -387,7 +387,8 @@ def test_latent_attention_and_delta_rule_over_page_borders(dtype):
 def test_fast_attention_paths_agree_with_the_general_kernel():
     """In bfloat16, with keys and values of 64 entries per head, prompts of both attention mixers take the tiled
     kernel (32-bit weights as three bfloat16 terms; the latent mixer over per-head keys and values of the step's own)
-    and single tokens of the plain attention mixer take the CUDA-core decode kernel.  The general kernel on the same
+    and single tokens take the CUDA-core decode kernel (plain attention) or the kernel that serves all heads from one
+    pass over the latent rows (latent attention).  The general kernel on the same
     rows gives the same up to the rounding of bfloat16 intermediates, for sequences that end at a page's edge,
     inside a page, and, where the path allows it, with cached positions in front."""
     name, dtype = "wide", "bfloat16"
@@ -406,7 +407,8 @@ def test_fast_attention_paths_agree_with_the_general_kernel():
             delattr(mixer, switch)
         return fast, general
 
-    assert model.layers[0].mixer._tiled() and model.layers[2].mixer._exact_tiled() and model.layers[2].mixer._exact_decode()
+    assert model.layers[0].mixer._tiled() and model.layers[0].mixer._fast_decode()
+    assert model.layers[2].mixer._exact_tiled() and model.layers[2].mixer._exact_decode()
     for layer, switch, steps in ((0, "_tiled", [[130, 64, 3]]), (2, "_exact_tiled", [[130, 64, 3], [70, 1, 129]])):
         slots = [eng.open() for _ in range(3)]
         for lens in steps:
@@ -417,11 +419,11 @@ def test_fast_attention_paths_agree_with_the_general_kernel():
             fast, general = both(layer, h, ctx, switch)
             eng.cache.advance(slots, lens)
             assert float((fast - general).abs().max()) <= 2 ** -5 * float(general.abs().max()), (layer, lens)
-        if layer == 2:
-            h = torch.randn(3, cfg["width"], generator=g).to(torch.bfloat16).to(DEV)
-            ctx, _, _ = eng.plan([entry(s, [1], ()) for s in slots])
-            fast, general = both(layer, h, ctx, "_exact_decode")
-            assert float((fast - general).abs().max()) <= 2 ** -6 * float(general.abs().max())
+        # single tokens: the CUDA-core decode kernel (attention), the kernel that serves all heads from one pass (latent)
+        h = torch.randn(3, cfg["width"], generator=g).to(torch.bfloat16).to(DEV)
+        ctx, _, _ = eng.plan([entry(s, [1], ()) for s in slots])
+        fast, general = both(layer, h, ctx, "_exact_decode" if layer == 2 else "_fast_decode")
+        assert float((fast - general).abs().max()) <= 2 ** -6 * float(general.abs().max()), layer
         for s_ in slots:
             eng.close(s_)
 
