@@ -3,7 +3,8 @@
 // brought into that space (q' = W_uk^T q, then the rotated part).  score_h(j) = q_h . row_j * scale over the
 // C + R entries; the mix of values is the mix of the rows' first C entries.
 //
-// One block per (token, split of the token's keys) serves ALL heads from one pass over its keys: 32 rows at a
+// Two kernels follow, both with one block per (token, split of the token's keys) that serves ALL heads from one
+// pass over its keys; the second, on the tensor cores, is taken where its sizes fit.  The first: 32 rows at a
 // time are copied into shared memory once (16-byte pieces, rows padded by 16 bytes so that lanes reading
 // different rows fall into different banks) and every warp takes its heads (warp, warp + 8, ...) over them:
 // lane = key for the scores, lane = pair of entries for the values.  The general kernel, with a block per
@@ -136,6 +137,173 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(const LdParam
     }
 }
 
+// ---------------------------------------------------------------- the same on the tensor cores
+// The heads of a token are the 16 rows of mma.sync m16n8k16 tiles (heads beyond H are rows of zeros).  Four
+// warps: each computes all scores of the 32 keys (S = Q K^T over the C + R entries: cheap, and it spares an
+// exchange), does the softmax of its two rows per thread in registers, and multiplies the weights with its own
+// quarter of the value columns.  The weights stay 32-bit: each is split into three bfloat16 terms (hi + mid +
+// lo = the float exactly), three products with the same V fragments, sums in 32-bit.  Scores are 32-bit sums of
+// exact products of bfloat16 q and rows.  Needs (C + R) % 16 == 0 and C % 64 == 0.
+constexpr int LM_THREADS = 128;
+constexpr int LM_MAX_OT = LD_MAX_C / 4 / 8;          // value tiles of 8 columns per warp
+
+__device__ __forceinline__ void lm_ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    unsigned a = unsigned(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lm_ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    unsigned a = unsigned(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lm_mma(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned lm_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void lm_split3(float p, float& hi, float& mid, float& lo) {
+    hi = __bfloat162float(__float2bfloat16_rn(p));
+    const float r1 = p - hi;
+    mid = __bfloat162float(__float2bfloat16_rn(r1));
+    lo = r1 - mid;
+}
+
+__global__ void __launch_bounds__(LM_THREADS) latent_decode_mma_kernel(const LdParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int t = blockIdx.x, split = blockIdx.y;
+    const int b = p.seq_of[t];
+    if (b < 0) return;
+    const int H = p.H, C = p.C, HDK = p.C + p.R, KS = ld_row_stride(HDK);
+    __nv_bfloat16* qt = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [16][KS]: the heads' queries
+    __nv_bfloat16* kt = qt + 16 * KS;                                          // [32][KS]: 32 cached rows
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = p.pos[t];
+    const int nkb = (pos >> 5) + 1;
+    const int per = (nkb + p.splits - 1) / p.splits;
+    const int kb0 = split * per, kb1 = min(nkb, kb0 + per);
+    const int* trow = p.table + size_t(b) * p.table_width;
+    const int pieces = HDK / 8;
+    for (int i = threadIdx.x; i < 16 * pieces; i += LM_THREADS) {
+        const int r = i / pieces, c8 = i - r * pieces;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < H) v = *reinterpret_cast<const uint4*>(p.q + size_t(t) * p.ldq + size_t(r) * HDK + 8 * c8);
+        *reinterpret_cast<uint4*>(qt + r * KS + 8 * c8) = v;
+    }
+    const int CW = C / 4, ot = CW / 8;                 // this warp's value columns [warp * CW, +CW): ot tiles of 8
+    const float sl2 = p.scale * 1.4426950408889634f;
+    float o[LM_MAX_OT][4];
+#pragma unroll
+    for (int i = 0; i < LM_MAX_OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    for (int kb = kb0; kb < kb1; ++kb) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 32 * pieces; i += LM_THREADS) {
+            const int r = i / pieces, c8 = i - r * pieces, j = kb * 32 + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (j <= pos) v = *reinterpret_cast<const uint4*>(p.cache + gb_kv_offset(trow, p.ring_pages, j, 0, 1, HDK) + 8 * c8);
+            *reinterpret_cast<uint4*>(kt + r * KS + 8 * c8) = v;
+        }
+        __syncthreads();
+        // ---- S = Q K^T: 16 heads x 32 keys, as four tiles of 8 keys
+        float s[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        for (int k = 0; k < HDK / 16; ++k) {
+            unsigned qf[4];
+            lm_ldmatrix_x4(qf[0], qf[1], qf[2], qf[3], qt + (lane & 15) * KS + 16 * k + 8 * (lane >> 4));
+#pragma unroll
+            for (int j2 = 0; j2 < 2; ++j2) {
+                unsigned b0, b1, b2, b3;
+                lm_ldmatrix_x4(b0, b1, b2, b3, kt + (j2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + 16 * k + 8 * ((lane >> 3) & 1));
+                lm_mma(s[2 * j2], qf[0], qf[1], qf[2], qf[3], b0, b1);
+                lm_mma(s[2 * j2 + 1], qf[0], qf[1], qf[2], qf[3], b2, b3);
+            }
+        }
+        // ---- mask and running softmax: this thread's rows are heads lane / 4 and lane / 4 + 8
+        const int key0 = kb * 32 + 2 * (lane & 3);
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int ka = key0 + 8 * j;
+            if (ka > pos) s[j][0] = s[j][2] = -INFINITY;
+            if (ka + 1 > pos) s[j][1] = s[j][3] = -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);       // finite: key kb * 32 is never masked
+        const float a0 = m0 == -INFINITY ? 0.f : exp2f((m0 - mn0) * sl2), a1 = m1 == -INFINITY ? 0.f : exp2f((m1 - mn1) * sl2);
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            s[j][0] = exp2f((s[j][0] - mn0) * sl2); s[j][1] = exp2f((s[j][1] - mn0) * sl2);
+            s[j][2] = exp2f((s[j][2] - mn1) * sl2); s[j][3] = exp2f((s[j][3] - mn1) * sl2);
+            sum0 += s[j][0] + s[j][1];
+            sum1 += s[j][2] + s[j][3];
+        }
+        l0 = l0 * a0 + sum0;
+        l1 = l1 * a1 + sum1;
+        m0 = mn0;
+        m1 = mn1;
+#pragma unroll
+        for (int i = 0; i < LM_MAX_OT; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+        // ---- O += P V over this warp's columns; the weights as three bfloat16 terms, smallest first
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            unsigned ph[4], pm[4], pl[4];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float h4[4], m4[4], l4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) lm_split3(s[2 * kk + half][e], h4[e], m4[e], l4[e]);
+                ph[2 * half] = lm_pack(h4[0], h4[1]); ph[2 * half + 1] = lm_pack(h4[2], h4[3]);
+                pm[2 * half] = lm_pack(m4[0], m4[1]); pm[2 * half + 1] = lm_pack(m4[2], m4[3]);
+                pl[2 * half] = lm_pack(l4[0], l4[1]); pl[2 * half + 1] = lm_pack(l4[2], l4[3]);
+            }
+#pragma unroll
+            for (int i2 = 0; i2 < LM_MAX_OT / 2; ++i2) {
+                if (2 * i2 < ot) {
+                    unsigned b0, b1, b2, b3;
+                    lm_ldmatrix_x4_trans(b0, b1, b2, b3, kt + (kk * 16 + (lane & 15)) * KS + warp * CW + 16 * i2 + 8 * (lane >> 4));
+                    lm_mma(o[2 * i2], pl[0], pl[1], pl[2], pl[3], b0, b1);
+                    lm_mma(o[2 * i2 + 1], pl[0], pl[1], pl[2], pl[3], b2, b3);
+                    lm_mma(o[2 * i2], pm[0], pm[1], pm[2], pm[3], b0, b1);
+                    lm_mma(o[2 * i2 + 1], pm[0], pm[1], pm[2], pm[3], b2, b3);
+                    lm_mma(o[2 * i2], ph[0], ph[1], ph[2], ph[3], b0, b1);
+                    lm_mma(o[2 * i2 + 1], ph[0], ph[1], ph[2], ph[3], b2, b3);
+                }
+            }
+        }
+    }
+    // ---- this split's unnormalised mix, maximum (in units of the exponent) and sum
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int h0 = lane >> 2, h1 = h0 + 8;
+    float* o0 = p.scratch + ((size_t(t) * H + h0) * p.splits + split) * (C + 2);
+    float* o1 = p.scratch + ((size_t(t) * H + h1) * p.splits + split) * (C + 2);
+#pragma unroll
+    for (int i = 0; i < LM_MAX_OT; ++i) {
+        if (i < ot) {
+            const int c = warp * CW + 8 * i + 2 * (lane & 3);
+            if (h0 < H) { o0[c] = o[i][0]; o0[c + 1] = o[i][1]; }
+            if (h1 < H) { o1[c] = o[i][2]; o1[c + 1] = o[i][3]; }
+        }
+    }
+    if (warp == 0 && (lane & 3) == 0) {
+        if (h0 < H) { o0[C] = m0 == -INFINITY ? -INFINITY : m0 * p.scale; o0[C + 1] = l0; }
+        if (h1 < H) { o1[C] = m1 == -INFINITY ? -INFINITY : m1 * p.scale; o1[C + 1] = l1; }
+    }
+}
+
 // out[t, h, :] = sum_s mix_s e^(m_s - M) / sum_s l_s e^(m_s - M), splits in order; padding tokens give zeros.
 __global__ void latent_decode_merge_kernel(const float* __restrict__ scratch, const int* __restrict__ seq_of,
                                            __nv_bfloat16* __restrict__ out, long long ldo, int H, int C, int splits) {
@@ -171,6 +339,17 @@ GB_API int gb_latent_decode_supported(int H, int C, int R, int q_dtype, int cach
            (C + R) % 8 == 0 && smem <= 160 * 1024;
 }
 
+// The tensor-core kernel takes what the kernel above takes when also (C + R) % 16 == 0 and C % 64 == 0.
+static bool latent_decode_mma_fits(int H, int C, int R) {
+    return H <= 16 && (C + R) % 16 == 0 && C % 64 == 0 && C <= LD_MAX_C && size_t(48) * ld_row_stride(C + R) * 2 <= 96 * 1024;
+}
+
+static int g_latent_decode_mma = 1;
+GB_API int gb_latent_decode_set_mma(int on) {
+    g_latent_decode_mma = on;
+    return 0;
+}
+
 GB_API long long gb_latent_decode_scratch_floats(int T, int H, int C, int splits) {
     return (long long)T * H * splits * (C + 2);
 }
@@ -189,6 +368,20 @@ GB_API int gb_latent_decode(const void* q, long long ldq, void* out, long long l
     p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.seq_of = seq_of; p.pos = pos; p.table = table;
     p.scratch = scratch; p.ldq = ldq; p.H = H; p.C = C; p.R = R; p.splits = splits; p.table_width = table_width;
     p.ring_pages = ring_pages; p.scale = scale;
+    if (g_latent_decode_mma && latent_decode_mma_fits(H, C, R)) {
+        const size_t smem_mma = size_t(48) * ld_row_stride(C + R) * 2;
+        static bool configured_mma = false;
+        if (smem_mma > 48 * 1024 && !configured_mma) {
+            if (cudaFuncSetAttribute(latent_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+                return gb_fail("gb_latent_decode: cannot get %zu bytes of shared memory", smem_mma);
+            configured_mma = true;
+        }
+        latent_decode_mma_kernel<<<dim3(T, splits), LM_THREADS, smem_mma, stream>>>(p);
+        GB_LAUNCH_OK("gb_latent_decode (tensor cores)");
+        latent_decode_merge_kernel<<<dim3(T, H), 128, 0, stream>>>(scratch, seq_of, (__nv_bfloat16*)out, ldo, H, C, splits);
+        GB_LAUNCH_OK("gb_latent_decode (merge)");
+        return 0;
+    }
     const size_t smem = size_t(H) * (C + R) * 4 + size_t(32) * ld_row_stride(C + R) * 2;
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {

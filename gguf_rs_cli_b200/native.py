@@ -151,6 +151,7 @@ _SIGNATURES = {
     "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _P],
     "gb_pack_latent_heads": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
     "gb_latent_decode_supported": [_I, _I, _I, _I, _I],
+    "gb_latent_decode_set_mma": [_I],
     "gb_latent_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_latent_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P],
     "gb_head_matmul": [_P, _I, _L, _I, _P, _I, _I, _I, _I, _P, _I, _L, _I, _I, _P],

@@ -424,6 +424,15 @@ def test_fast_attention_paths_agree_with_the_general_kernel():
         ctx, _, _ = eng.plan([entry(s, [1], ()) for s in slots])
         fast, general = both(layer, h, ctx, "_exact_decode" if layer == 2 else "_fast_decode")
         assert float((fast - general).abs().max()) <= 2 ** -6 * float(general.abs().max()), layer
+        if layer == 0:
+            # the same without the tensor-core kernel: the CUDA-core kernel of one pass for all heads
+            from gguf_rs_cli_b200 import native
+            native.library().gb_latent_decode_set_mma(0)
+            try:
+                plain = model.layers[0].mixer.forward(h, ctx, eng.runs[0]).float().clone()
+            finally:
+                native.library().gb_latent_decode_set_mma(1)
+            assert float((plain - general).abs().max()) <= 2 ** -6 * float(general.abs().max())
         for s_ in slots:
             eng.close(s_)
 
