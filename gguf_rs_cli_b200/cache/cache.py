@@ -10,7 +10,9 @@ or be left out where a mixer finds them in its key rows).  A sequence's position
 pages through its page table; a windowed group keeps only a ring of pages per
 sequence (position p lives in table entry (p // PAGE) % ring_pages), sized so that
 every key a step can still need is resident: window + the longest step - 1
-positions.  What a slot holds is valid up to its length; pages and state are given
+positions.  A windowed group whose mixer keeps the sequence's first positions visible for
+ever (`keep_first`) holds the pages of those positions in the first `head_pages` entries
+of the table, which are never written again, and the ring in the entries behind them.  What a slot holds is valid up to its length; pages and state are given
 back when the sequence is closed and are used again without being cleared, except
 the fixed-size state, which is zeroed when a slot is opened.
 
@@ -33,6 +35,7 @@ class KVSpec:
     window: Optional[int] = None        # None: all keys; W: the last W positions
     v_dim: Optional[int] = None         # entries of a value: None as head_dim; 0: no values are kept (a mixer
                                         # whose values are part of its key rows)
+    keep_first: int = 0                 # with a window: the first positions of a sequence that stay for ever
 
 
 @dataclass
@@ -44,16 +47,18 @@ class CacheLayout:
 
 
 class KVGroup:
-    def __init__(self, index: int, spec: KVSpec, runs: List[int], n_pages: int, ring_pages: int, table_width: int):
+    def __init__(self, index: int, spec: KVSpec, runs: List[int], n_pages: int, ring_pages: int, table_width: int,
+                 head_pages: int = 0):
         self.index, self.spec, self.runs = index, spec, runs
         self.n_pages, self.ring_pages, self.table_width = n_pages, ring_pages, table_width
+        self.head_pages = head_pages                    # table entries in front of the ring (kept first positions)
         self.pool = FreeList(n_pages, f"page of group {index}")
         self.tables: Dict[int, List[int]] = {}
         self.k = None
         self.v = None
 
     def pages_needed(self, length: int) -> int:
-        return min(pages_for(length), self.ring_pages)
+        return min(pages_for(length), self.head_pages + self.ring_pages)
 
 
 class Cache:
@@ -81,12 +86,14 @@ class Cache:
             by_spec.setdefault(layout.kv[run], []).append(run)
         width = min(self.n_pages, pages_for(self.max_len))
         for spec, runs in by_spec.items():
+            head = 0
             if spec.window is None:
                 ring, n_pages = width, self.n_pages
             else:
-                ring = min(width, pages_for(spec.window + self.max_step_tokens - 1) + 1)
-                n_pages = min(self.n_pages, self.n_slots * ring)
-            g = KVGroup(len(self.groups), spec, runs, n_pages, ring, min(width, ring))
+                head = min(pages_for(spec.keep_first), width - 1) if spec.keep_first else 0
+                ring = min(width - head, pages_for(spec.window + self.max_step_tokens - 1) + 1)
+                n_pages = min(self.n_pages, self.n_slots * (head + ring))
+            g = KVGroup(len(self.groups), spec, runs, n_pages, ring, min(width, head + ring), head)
             for i, run in enumerate(runs):
                 self.group_of_run[run] = (g.index, i)
             self.groups.append(g)
@@ -210,6 +217,6 @@ class Cache:
                     seen.add(p)
                 # a reservation made for a step that has not been counted yet may hold more pages than the
                 # length needs, never fewer and never more than the ring
-                assert g.pages_needed(self.lengths[s]) <= len(pages) <= g.ring_pages, \
+                assert g.pages_needed(self.lengths[s]) <= len(pages) <= g.head_pages + g.ring_pages, \
                     f"slot {s} of length {self.lengths[s]} holds {len(pages)} pages of group {g.index}"
             assert len(seen) == g.pool.held_count, f"group {g.index}: {g.pool.held_count - len(seen)} pages are lost"

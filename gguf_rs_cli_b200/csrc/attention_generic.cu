@@ -7,7 +7,10 @@
 // blocks of 32 absolute positions, warp w taking blocks w, w+8, ..., and the eight
 // partial results are merged in warp order, so a token's result depends on nothing but
 // its own query and keys.  It is the attention of the 32-bit mode, the twin of the
-// faster kernels in tests, and the path for head sizes those refuse.
+// faster kernels in tests, and the path for head sizes those refuse.  Options: the first
+// keep_first positions of a sequence stay visible behind the window (their pages are the
+// first head_pages entries of the page table, in front of the ring); the result is
+// multiplied by sigmoid(gate) entry by entry.
 #include <math.h>
 
 #include "common.cuh"
@@ -23,7 +26,8 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     const void* __restrict__ q, int q_dtype, long long ldq, void* __restrict__ out, int out_dtype, long long ldo,
     int nh, int nkv, int hd, int hdv, int v_row, const int* __restrict__ seq_of, const int* __restrict__ pos,
     const int* __restrict__ table, int table_width, int ring_pages, const TC* __restrict__ kc,
-    const TC* __restrict__ vc, int window, float scale) {
+    const TC* __restrict__ vc, int window, float scale, int head_pages, int keep_first, const void* __restrict__ gate,
+    int gate_dtype, long long ldg) {
     int t = blockIdx.x, h = blockIdx.y;
     int b = seq_of[t];
     size_t orow = size_t(t) * ldo + size_t(h) * hdv;
@@ -63,12 +67,17 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
             for (int e = 0; e < 8; ++e) qr[c][e] = (lane + 32 * c) * 8 < hd ? qs[(lane + 32 * c) * 8 + e] : 0.f;
     }
 
-    for (int kb = (lo >> 5) + warp; kb <= (p >> 5); kb += AG_WARPS) {
-        int j = kb * 32 + lane;
-        bool valid = j >= lo && j <= p;
+    // The keys a token sees: the window [lo, p], and in front of it the sequence's first keep_first positions as far as
+    // the window does not hold them, [0, kept).  Blocks of the kept keys come first in the warps' round.
+    const int kept = min(keep_first, lo), kept_blocks = (kept + 31) >> 5;
+    const int n_blocks = kept_blocks + (p >> 5) - (lo >> 5) + 1;
+    for (int ib = warp; ib < n_blocks; ib += AG_WARPS) {
+        const bool front = ib < kept_blocks;
+        int j = (front ? ib : (lo >> 5) + ib - kept_blocks) * 32 + lane;
+        bool valid = front ? j < kept : (j >= lo && j <= p);
         float s = -INFINITY;
         long long off = 0;
-        if (valid) off = (long long)gb_kv_offset(trow, ring_pages, j, g, nkv, 1);        // the position's row number
+        if (valid) off = (long long)gb_kv_offset(trow, ring_pages, j, g, nkv, 1, head_pages);        // the position's row number
         if (shared_rows) {
             const unsigned live = __ballot_sync(0xffffffffu, valid);
             for (int jj = 0; jj < 32; jj += 2) {
@@ -155,7 +164,9 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
     for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < AG_WARPS; ++w) o += acc_s[w][d] * wgt[w];
-        gb_store(out, out_dtype, orow + d, o / L);
+        o /= L;
+        if (gate) o *= 1.f / (1.f + expf(-gb_load(gate, gate_dtype, size_t(t) * ldg + size_t(h) * hdv + d)));
+        gb_store(out, out_dtype, orow + d, o);
     }
 }
 
@@ -166,19 +177,22 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(
 GB_API int gb_attention_generic(const void* q, int q_dtype, long long ldq, void* out, int out_dtype, long long ldo,
                                 int T, int nh, int nkv, int hd, int hdv, int v_row, const int* seq_of, const int* pos,
                                 const int* table, int table_width, int ring_pages, const void* kcache,
-                                const void* vcache, int cache_dtype, int window, float scale, cudaStream_t stream) {
+                                const void* vcache, int cache_dtype, int window, float scale, int head_pages, int keep_first,
+                                const void* gate, int gate_dtype, long long ldg, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(q_dtype) && gb_is_dtype(out_dtype) && gb_is_dtype(cache_dtype), "gb_attention_generic: bad dtype");
     GB_REQUIRE(hd > 0 && hd <= AG_MAX_HD, "gb_attention_generic: head_dim %d is not in 1..%d", hd, AG_MAX_HD);
     GB_REQUIRE(hdv > 0 && hdv <= AG_MAX_HD && v_row >= hdv, "gb_attention_generic: value size %d (rows of %d) is not in 1..%d", hdv, v_row, AG_MAX_HD);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_generic: %d heads are not a multiple of %d KV heads", nh, nkv);
     GB_REQUIRE(nh <= 65535, "gb_attention_generic: too many heads (%d)", nh);
-    GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0, "gb_attention_generic: bad cache geometry");
+    GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && head_pages >= 0, "gb_attention_generic: bad cache geometry");
+    GB_REQUIRE(keep_first >= 0 && (window == 0 || keep_first <= head_pages * GB_PAGE), "gb_attention_generic: %d kept positions need more than %d kept pages", keep_first, head_pages);
+    GB_REQUIRE(!gate || gb_is_dtype(gate_dtype), "gb_attention_generic: bad gate dtype");
     if (T == 0) return 0;
     dim3 grid(T, nh);
 #define AG_LAUNCH(TC, MAX_HD)                                                                                     \
     attention_generic_kernel<TC, MAX_HD><<<grid, AG_WARPS * 32, 0, stream>>>(                                     \
         q, q_dtype, ldq, out, out_dtype, ldo, nh, nkv, hd, hdv, v_row, seq_of, pos, table, table_width, ring_pages, \
-        (const TC*)kcache, (const TC*)vcache, window, scale)
+        (const TC*)kcache, (const TC*)vcache, window, scale, head_pages, window > 0 ? keep_first : 0, gate, gate_dtype, ldg)
     const bool small = hd <= 256 && hdv <= 256;
     if (cache_dtype == GB_F32) {
         if (small) AG_LAUNCH(float, 256);

@@ -270,3 +270,116 @@ GB_API int gb_head_matmul(const void* x, int x_dtype, long long ldx, int xs, con
     GB_LAUNCH_OK("gb_head_matmul");
     return 0;
 }
+
+// ------------------------- per-head RMS norm with a weight, rotation, mixing of values, cache write
+// One block per token; its warps take the token's heads in turn: q heads (treated in place), k heads (into the
+// cache), v heads (into the cache).
+//   q_h <- rot_p(q_h / sqrt(mean(q_h^2) + eps) * wq),  k_g likewise with wk       (wq, wk [D] serve all heads;
+//                                                                                  null: no norm at all)
+//   rot_p: the first rot_dims entries of a head in pairs, (i, i + rot_dims/2) or (2i, 2i+1), by the angle
+//          p * inv_freq[i]; the other entries pass; inv_freq null: no rotation
+//   v_g <- (1 - lambda) v_g + lambda v_first_g   when v_first is given (another layer's values of the same token);
+//   first_out, when given, receives the token's own values as they came (for the layers that mix them in).
+// A head lies in shared memory (32-bit) between the norm and the rotation.  Cache positions follow the page table
+// with head_pages kept pages in front of the ring.
+struct HeadPrepParams {
+    void* q;
+    const void *k, *v;
+    long long ld;
+    int dtype, H, G, D, Dv;
+    const void *wq, *wk;
+    int w_dtype;
+    float eps;
+    const float* inv_freq;
+    int rot_dims, pairing;
+    const void* v_first;
+    long long ld_first;
+    float lambda;
+    void* first_out;
+    long long ld_out;
+    const int *seq_of, *pos, *table;
+    int table_width, ring_pages, head_pages;
+    void *kcache, *vcache;
+    int cache_dtype;
+};
+
+__global__ void __launch_bounds__(128) head_prep_kv_write_kernel(const HeadPrepParams a) {
+    extern __shared__ float hp_sm[];
+    const int t = blockIdx.x;
+    const int b = a.seq_of[t];
+    if (b < 0) return;
+    const int p = a.pos[t];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int H = a.H, G = a.G, D = a.D, Dv = a.Dv;
+    float* buf = hp_sm + warp * D;
+    const size_t row = size_t(t) * size_t(a.ld);
+    const int* trow = a.table + size_t(b) * a.table_width;
+    const int half = a.inv_freq ? a.rot_dims / 2 : 0;
+    for (int item = warp; item < H + 2 * G; item += warps) {
+        if (item < H + G) {
+            const bool is_q = item < H;
+            const void* src = is_q ? (const void*)a.q : a.k;
+            const void* w = is_q ? a.wq : a.wk;
+            const size_t o = row + size_t(is_q ? item : item - H) * D;
+            float ss = 0.f;
+            for (int d = lane; d < D; d += 32) {
+                const float x = gb_load(src, a.dtype, o + d);
+                buf[d] = x;
+                ss = fmaf(x, x, ss);
+            }
+            if (w) {
+                const float f = 1.f / sqrtf(gb_warp_sum(ss) / float(D) + a.eps);
+                for (int d = lane; d < D; d += 32) buf[d] = buf[d] * f * gb_load(w, a.w_dtype, d);
+            }
+            __syncwarp();
+            void* dst = is_q ? a.q : a.kcache;
+            const int dt = is_q ? a.dtype : a.cache_dtype;
+            const size_t c = is_q ? o : gb_kv_offset(trow, a.ring_pages, p, item - H, G, D, a.head_pages);
+            for (int i = lane; i < half; i += 32) {
+                const int d0 = a.pairing ? 2 * i : i, d1 = a.pairing ? 2 * i + 1 : i + half;
+                float sn, cs, y0, y1;
+                sincosf(float(p) * a.inv_freq[i], &sn, &cs);
+                gb_rotate(buf[d0], buf[d1], cs, sn, y0, y1);
+                gb_store(dst, dt, c + d0, y0);
+                gb_store(dst, dt, c + d1, y1);
+            }
+            for (int d = 2 * half + lane; d < D; d += 32) gb_store(dst, dt, c + d, buf[d]);
+            __syncwarp();
+        } else {
+            const int g = item - H - G;
+            const size_t o = row + size_t(g) * Dv;
+            const size_t c = gb_kv_offset(trow, a.ring_pages, p, g, G, Dv, a.head_pages);
+            for (int d = lane; d < Dv; d += 32) {
+                float x = gb_load(a.v, a.dtype, o + d);
+                if (a.first_out) gb_store(a.first_out, a.dtype, size_t(t) * a.ld_out + size_t(g) * Dv + d, x);
+                if (a.v_first) x = (1.f - a.lambda) * x + a.lambda * gb_load(a.v_first, a.dtype, size_t(t) * a.ld_first + size_t(g) * Dv + d);
+                gb_store(a.vcache, a.cache_dtype, c + d, x);
+            }
+        }
+    }
+}
+
+// q [T, H*D] (treated in place), k [T, G*D], v [T, G*Dv]: column slices of one row-major buffer, rows `ld` apart.
+// kcache [pages, G, PAGE, D], vcache [pages, G, PAGE, Dv].  v_first, first_out: [T, G*Dv] with rows of their own.
+GB_API int gb_head_prep_kv_write(void* q, const void* k, const void* v, int dtype, long long ld, int T, int H, int G, int D,
+                                 int Dv, const void* wq, const void* wk, int w_dtype, float eps, const float* inv_freq,
+                                 int rot_dims, int pairing, const void* v_first, long long ld_first, float lambda,
+                                 void* first_out, long long ld_out, const int* seq_of, const int* pos, const int* table,
+                                 int table_width, int ring_pages, int head_pages, void* kcache, void* vcache,
+                                 int cache_dtype, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(cache_dtype), "gb_head_prep_kv_write: bad dtype");
+    GB_REQUIRE(H > 0 && G > 0 && D > 0 && Dv > 0 && D <= 4096, "gb_head_prep_kv_write: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d", H, G, D, Dv);
+    GB_REQUIRE((wq == nullptr) == (wk == nullptr) && (!wq || (gb_is_dtype(w_dtype) && eps > 0.f)), "gb_head_prep_kv_write: bad norm");
+    GB_REQUIRE(!inv_freq || (rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= D), "gb_head_prep_kv_write: %d of %d entries cannot be rotated", rot_dims, D);
+    GB_REQUIRE(q && k && v && table && kcache && vcache && ring_pages > 0 && head_pages >= 0 && table_width >= 1, "gb_head_prep_kv_write: arguments missing");
+    if (T == 0) return 0;
+    HeadPrepParams a;
+    a.q = q; a.k = k; a.v = v; a.ld = ld; a.dtype = dtype; a.H = H; a.G = G; a.D = D; a.Dv = Dv; a.wq = wq; a.wk = wk;
+    a.w_dtype = w_dtype; a.eps = eps; a.inv_freq = inv_freq; a.rot_dims = rot_dims; a.pairing = pairing; a.v_first = v_first;
+    a.ld_first = ld_first; a.lambda = lambda; a.first_out = first_out; a.ld_out = ld_out; a.seq_of = seq_of; a.pos = pos;
+    a.table = table; a.table_width = table_width; a.ring_pages = ring_pages; a.head_pages = head_pages; a.kcache = kcache;
+    a.vcache = vcache; a.cache_dtype = cache_dtype;
+    head_prep_kv_write_kernel<<<T, 128, size_t(4) * D * sizeof(float), stream>>>(a);
+    GB_LAUNCH_OK("gb_head_prep_kv_write");
+    return 0;
+}

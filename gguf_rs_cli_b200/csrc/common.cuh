@@ -81,11 +81,20 @@ __device__ __forceinline__ void gb_store(void* p, int dtype, size_t i, float v) 
     else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
 }
 
+// Entry of a sequence's page table that holds position `pos`: the sequence's first head_pages pages are kept
+// for ever (entries 0 .. head_pages - 1), the pages after them go round a ring of ring_pages entries behind
+// those.  head_pages 0: the ring alone.
+__device__ __forceinline__ int gb_table_entry(int pos, int ring_pages, int head_pages) {
+    const int pg = pos >> GB_PAGE_SHIFT;
+    return pg < head_pages ? pg : head_pages + (pg - head_pages) % ring_pages;
+}
+
 // Where position `pos` of the sequence with page-table row `row` lives: element offset
 // of [kv head g][pos % PAGE][0] inside one run's K or V storage
 // [pages][kv heads][PAGE][head_dim].
-__device__ __forceinline__ size_t gb_kv_offset(const int* row, int ring_pages, int pos, int g, int nkv, int hd) {
-    int page = row[(pos >> GB_PAGE_SHIFT) % ring_pages];
+__device__ __forceinline__ size_t gb_kv_offset(const int* row, int ring_pages, int pos, int g, int nkv, int hd,
+                                               int head_pages = 0) {
+    int page = row[gb_table_entry(pos, ring_pages, head_pages)];
     return ((size_t(page) * nkv + g) * GB_PAGE + (pos & (GB_PAGE - 1))) * size_t(hd);
 }
 
@@ -102,6 +111,20 @@ enum GbGateAct { GB_ACT_SILU = 1, GB_ACT_GELU_TANH = 2 };
 __device__ __forceinline__ float gb_gate_act(float z, int act) {
     if (act == GB_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     return z / (1.f + expf(-z));
+}
+
+// A gated unit with clamped inputs: g <- min(g, limit), u <- clamp(u, -limit, limit), g sigmoid(1.702 g) (u + 1).
+__device__ __forceinline__ float gb_act_glu_clamped(float g, float u, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
+// Activations of one value: 3 GELU in its exact form 0.5 z (1 + erf(z / sqrt 2)); else as gb_gate_act.
+enum GbUnaryAct { GB_ACT_GELU_ERF = 3 };
+__device__ __forceinline__ float gb_act_unary(float z, int act) {
+    if (act == GB_ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+    return gb_gate_act(z, act);
 }
 
 __device__ __forceinline__ float gb_warp_sum(float v) {

@@ -397,11 +397,12 @@ GB_API int gb_delta_rule(const void* q, const void* k, const void* v, int dtype,
 }
 
 // --------------------------------------------- per-head RMS norm, weight, gate
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w[:] * sigmoid(gate[t, h, :]); one warp per
-// (token, head); w [Dv] is shared by the heads.
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w[:] * f(gate[t, h, :]); one warp per
+// (token, head); w [Dv] is shared by the heads.  f: 0 the sigmoid, 1 SiLU (z sigmoid(z)).
 __global__ void gated_head_norm_kernel(const float* __restrict__ o, long long ldo, const void* __restrict__ gate,
                                        int gate_dtype, long long ldg, const void* __restrict__ w, int w_dtype, float eps,
-                                       void* __restrict__ out, int out_dtype, long long ld_out, long long items, int H, int Dv) {
+                                       void* __restrict__ out, int out_dtype, long long ld_out, long long items, int H, int Dv,
+                                       int gate_act) {
     const long long item = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= items) return;
     const int lane = threadIdx.x & 31;
@@ -414,19 +415,20 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, long long ld
     for (int d = lane; d < Dv; d += 32) {
         const float gt = gb_load(gate, gate_dtype, size_t(t) * ldg + size_t(h) * Dv + d);
         gb_store(out, out_dtype, size_t(t) * ld_out + size_t(h) * Dv + d,
-                 orow[d] / rms * gb_load(w, w_dtype, d) * (1.f / (1.f + expf(-gt))));
+                 orow[d] / rms * gb_load(w, w_dtype, d) * ((gate_act ? gt : 1.f) / (1.f + expf(-gt))));
     }
 }
 
 GB_API int gb_gated_head_norm(const float* o, long long ldo, const void* gate, int gate_dtype, long long ldg, const void* w,
                               int w_dtype, float eps, void* out, int out_dtype, long long ld_out, int T, int H, int Dv,
-                              cudaStream_t stream) {
+                              int gate_act, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(gate_dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(out_dtype), "gb_gated_head_norm: bad dtype");
     GB_REQUIRE(H > 0 && Dv > 0 && eps > 0.f, "gb_gated_head_norm: bad sizes heads=%d vdim=%d eps=%g", H, Dv, eps);
+    GB_REQUIRE(gate_act == 0 || gate_act == 1, "gb_gated_head_norm: unknown gate function %d", gate_act);
     if (T == 0) return 0;
     const long long items = (long long)T * H;
     gated_head_norm_kernel<<<unsigned((items + 3) / 4), 128, 0, stream>>>(o, ldo, gate, gate_dtype, ldg, w, w_dtype, eps, out,
-                                                                          out_dtype, ld_out, items, H, Dv);
+                                                                          out_dtype, ld_out, items, H, Dv, gate_act);
     GB_LAUNCH_OK("gb_gated_head_norm");
     return 0;
 }

@@ -1,0 +1,208 @@
+// Gated linear attention: per sequence and head a matrix S [D, Dv] (key channel i, value column j) that every
+// token first shrinks row by row and then adds an outer product to, and reads out with its query:
+//   alpha_i = sigmoid(z_i)^(1/tau) = exp(-softplus(-z_i) / tau),  z = a + bias      (32-bit)
+//   S_ij <- alpha_i S_ij + k_i v_j;   o_j = sum_i S_ij q_i
+// Two kernels, as for the delta rule (delta_rule.cu).  The first computes, for all tokens at once, what does not
+// depend on the state: scaled queries, keys, decays and values as 32-bit rows padded to a multiple of four
+// entries.  The second walks the tokens: a block takes a slice of columns of one (sequence, head); a column is
+// shared by R lanes of a warp (R a power of two), lane r holding the NR rows r*NR .. r*NR + NR - 1 in registers;
+// the read-out's sum over i ends with shuffles over those lanes.  The prepared rows of a few tokens at a time
+// are copied into shared memory with cp.async, the next chunk while this one is worked on.  The state is read
+// once at the start and written once at the end.
+#include <math.h>
+
+#include "common.cuh"
+
+struct GlaPrepParams {
+    const void *q, *k, *v;          // q, k [T, H*D], v [T, H*Dv]: column slices of one buffer, rows `ld` apart
+    const void* a;                  // [T, H*D] before the bias, rows ld_a apart
+    const void* bias;               // [H*D]
+    float* qkg;                     // [T, H, 3, DA]: scaled q, k, decays
+    float* vf;                      // [T, H, VA]
+    long long ld, ld_a;
+    int dtype, a_dtype, w_dtype, H, D, Dv, DA, VA;
+    float q_scale, inv_tau;
+};
+
+// One warp per (token, head).
+__global__ void __launch_bounds__(128) gla_prep_kernel(const GlaPrepParams p) {
+    const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (h >= p.H) return;
+    const int D = p.D, DA = p.DA;
+    float* o = p.qkg + (size_t(t) * p.H + h) * 3 * DA;
+    const size_t row = size_t(t) * p.ld + size_t(h) * D;
+    for (int d = lane; d < DA; d += 32) {
+        float qv = 0.f, kv = 0.f, gv = 0.f;
+        if (d < D) {
+            qv = gb_load(p.q, p.dtype, row + d) * p.q_scale;
+            kv = gb_load(p.k, p.dtype, row + d);
+            const float z = gb_load(p.a, p.a_dtype, size_t(t) * p.ld_a + size_t(h) * D + d) + gb_load(p.bias, p.w_dtype, size_t(h) * D + d);
+            const float sp = -z > 20.f ? -z : log1pf(expf(-z));          // softplus(-z) = -ln sigmoid(z)
+            gv = expf(-sp * p.inv_tau);
+        }
+        o[d] = qv;
+        o[DA + d] = kv;
+        o[2 * DA + d] = gv;
+    }
+    float* vo = p.vf + (size_t(t) * p.H + h) * p.VA;
+    for (int d = lane; d < p.VA; d += 32) vo[d] = d < p.Dv ? gb_load(p.v, p.dtype, size_t(t) * p.ld + size_t(h) * p.Dv + d) : 0.f;
+}
+
+struct GlaWalkParams {
+    const float *qkg, *vf;          // what gla_prep_kernel wrote
+    float* state;                   // [slots, H, D, Dv]
+    float* out;                     // [T, H*Dv], rows ldo apart
+    const int *cu, *slots, *qlens;
+    long long ldo;
+    int H, D, Dv, DA, VA, R, TC;
+};
+
+__device__ __forceinline__ void gla_cp16(float* dst, const float* src) {
+    unsigned d = unsigned(__cvta_generic_to_shared(dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int NR>
+__global__ void __launch_bounds__(128) gla_walk_kernel(const GlaWalkParams p) {
+    extern __shared__ __align__(16) float gla_sm[];
+    float* sm = gla_sm;
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int slot = p.slots[b], n = p.qlens[b];
+    if (slot < 0 || n <= 0) return;
+    const int R = p.R, CW = 32 / R, CB = 4 * CW, D = p.D, Dv = p.Dv, DA = p.DA, TC = p.TC;
+    const int RS = R * (NR + 4);                        // floats of one padded row of q, k or decays
+    const int TOK = 3 * RS + CB;                        // floats per token: q, k, decays, values of the slice
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane / CW, jj = lane - r * CW;
+    const int col0 = blockIdx.z * CB;
+    const int j = col0 + warp * CW + jj;
+    const bool col_ok = j < Dv;
+    float* sp = p.state + (size_t(slot) * p.H + h) * size_t(D) * Dv;
+    float S[NR];
+#pragma unroll
+    for (int m = 0; m < NR; ++m) {
+        const int i = r * NR + m;
+        S[m] = (i < D && col_ok) ? sp[size_t(i) * Dv + j] : 0.f;
+    }
+    for (int i = threadIdx.x; i < 2 * TC * TOK; i += 128) sm[i] = 0.f;      // what no copy reaches stays zero
+    __syncthreads();
+    const int t0 = p.cu[b];
+    const int q4 = DA / 4, v4 = max(0, min(CB, p.VA - col0)) / 4;         // 16-byte pieces per row
+    auto load_chunk = [&](int c0, int buf) {
+        const int nt = min(TC, n - c0);
+        float* base = sm + buf * TC * TOK;
+        const int per = 3 * q4 + v4;
+        for (int idx = threadIdx.x; idx < nt * per; idx += 128) {
+            const int tt = idx / per, e = idx - tt * per;
+            const size_t t = size_t(t0 + c0 + tt);
+            float* row = base + tt * TOK;
+            if (e < 3 * q4) {
+                const int which = e / q4, k4 = e - which * q4, i = 4 * k4;
+                gla_cp16(row + which * RS + (i / NR) * (NR + 4) + (i % NR), p.qkg + ((t * p.H + h) * 3 + which) * DA + i);
+            } else {
+                const int i = 4 * (e - 3 * q4);
+                gla_cp16(row + 3 * RS + i, p.vf + (t * p.H + h) * p.VA + col0 + i);
+            }
+        }
+    };
+    load_chunk(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    int buf = 0;
+    for (int c0 = 0; c0 < n; c0 += TC, buf ^= 1) {
+        const int nt = min(TC, n - c0);
+        if (c0 + TC < n) load_chunk(c0 + TC, buf ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const float* base = sm + buf * TC * TOK;
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* row = base + tt * TOK;
+            const float4* qq = reinterpret_cast<const float4*>(row + r * (NR + 4));
+            const float4* kk = reinterpret_cast<const float4*>(row + RS + r * (NR + 4));
+            const float4* gg = reinterpret_cast<const float4*>(row + 2 * RS + r * (NR + 4));
+            const float vj = row[3 * RS + warp * CW + jj];
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int m = 0; m < NR / 4; ++m) {
+                const float4 gv = gg[m], kv = kk[m], qv = qq[m];
+                S[4 * m] = fmaf(kv.x, vj, S[4 * m] * gv.x);         o0 = fmaf(S[4 * m], qv.x, o0);
+                S[4 * m + 1] = fmaf(kv.y, vj, S[4 * m + 1] * gv.y); o1 = fmaf(S[4 * m + 1], qv.y, o1);
+                S[4 * m + 2] = fmaf(kv.z, vj, S[4 * m + 2] * gv.z); o2 = fmaf(S[4 * m + 2], qv.z, o2);
+                S[4 * m + 3] = fmaf(kv.w, vj, S[4 * m + 3] * gv.w); o3 = fmaf(S[4 * m + 3], qv.w, o3);
+            }
+            float o = (o0 + o1) + (o2 + o3);
+            for (int off = CW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (r == 0 && col_ok) p.out[size_t(t0 + c0 + tt) * p.ldo + size_t(h) * Dv + j] = o;
+        }
+        __syncthreads();                                   // this buffer is loaded again two chunks on
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int m = 0; m < NR; ++m) {
+        const int i = r * NR + m;
+        if (i < D && col_ok) sp[size_t(i) * Dv + j] = S[m];
+    }
+}
+
+// Rows per lane and lanes per column for key size D (the delta rule's shapes).
+static void gla_shape(int D, int* nr, int* r) {
+    int NR = D > 1024 ? 64 : D > 64 ? 32 : D > 32 ? 16 : 8, R = 1;
+    while (R * NR < D) R <<= 1;
+    *nr = NR;
+    *r = R;
+}
+
+// Floats of scratch for the prepared rows of T tokens.
+GB_API long long gb_gla_scratch_floats(int T, int H, int D, int Dv) {
+    const long long DA = (D + 3) / 4 * 4, VA = (Dv + 3) / 4 * 4;
+    return (long long)T * H * (3 * DA + VA);
+}
+
+// q, k [T, H*D] and v [T, H*Dv]: column slices of one buffer with rows ld apart; a [T, H*D] the decay's
+// projection before its bias [H*D]; state [slots, H, D, Dv] float32, read and renewed; out float32 [T, H*Dv].
+GB_API int gb_gla(const void* q, const void* k, const void* v, int dtype, long long ld, const void* a, int a_dtype,
+                  long long ld_a, const void* bias, int w_dtype, float inv_tau, float q_scale, float* state, float* out,
+                  long long ldo, const int* cu, const int* slots, const int* qlens, int T, int B, int H, int D, int Dv,
+                  float* scratch, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(a_dtype) && gb_is_dtype(w_dtype), "gb_gla: bad dtype");
+    GB_REQUIRE(H > 0 && D > 0 && Dv > 0 && D <= 2048, "gb_gla: bad sizes heads=%d dim=%d vdim=%d (dim up to 2048)", H, D, Dv);
+    GB_REQUIRE(inv_tau > 0.f, "gb_gla: the decay's exponent must be positive");
+    GB_REQUIRE(scratch && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0, "gb_gla: scratch missing or misaligned");
+    if (B == 0 || T == 0) return 0;
+    const int DA = (D + 3) / 4 * 4, VA = (Dv + 3) / 4 * 4;
+    GlaPrepParams pp;
+    pp.q = q; pp.k = k; pp.v = v; pp.a = a; pp.bias = bias; pp.qkg = scratch; pp.vf = scratch + size_t(T) * H * 3 * DA;
+    pp.ld = ld; pp.ld_a = ld_a; pp.dtype = dtype; pp.a_dtype = a_dtype; pp.w_dtype = w_dtype; pp.H = H; pp.D = D; pp.Dv = Dv;
+    pp.DA = DA; pp.VA = VA; pp.q_scale = q_scale; pp.inv_tau = inv_tau;
+    GB_REQUIRE((H + 3) / 4 <= 65535, "gb_gla: too many heads (%d)", H);
+    gla_prep_kernel<<<dim3(T, (H + 3) / 4), 128, 0, stream>>>(pp);
+    GB_LAUNCH_OK("gb_gla (prepare)");
+    GlaWalkParams p;
+    p.qkg = pp.qkg; p.vf = pp.vf; p.state = state; p.out = out; p.cu = cu; p.slots = slots; p.qlens = qlens;
+    p.ldo = ldo; p.H = H; p.D = D; p.Dv = Dv; p.DA = DA; p.VA = VA;
+    int NR, R;
+    gla_shape(D, &NR, &R);
+    const int CB = 4 * (32 / R);
+    const int per_token = 4 * (3 * R * (NR + 4) + CB);
+    int TC = (20 * 1024) / per_token;                    // two buffers of at most 20 KB each
+    TC = TC < 1 ? 1 : (TC > 16 ? 16 : TC);
+    p.R = R; p.TC = TC;
+    const size_t smem = size_t(2) * TC * per_token;
+    GB_REQUIRE(smem <= 64 * 1024, "gb_gla: key size %d needs %zu bytes of shared memory", D, smem);
+    if (smem > 48 * 1024) {
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(gla_walk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+                return gb_fail("gb_gla: cannot get %zu bytes of shared memory", smem);
+            configured = true;
+        }
+    }
+    dim3 grid(B, H, (Dv + CB - 1) / CB);
+    GB_REQUIRE(grid.z <= 65535 && H <= 65535, "gb_gla: too many heads or value columns");
+    if (NR == 8) gla_walk_kernel<8><<<grid, 128, smem, stream>>>(p);
+    else if (NR == 16) gla_walk_kernel<16><<<grid, 128, smem, stream>>>(p);
+    else if (NR == 32) gla_walk_kernel<32><<<grid, 128, smem, stream>>>(p);
+    else gla_walk_kernel<64><<<grid, 128, smem, stream>>>(p);
+    GB_LAUNCH_OK("gb_gla");
+    return 0;
+}

@@ -1,0 +1,260 @@
+// A feed-forward of routed experts: the router's choice per token, and the chosen experts' gated units on the
+// CUDA cores with 32-bit sums, token by token (steps of few tokens, the 32-bit mode, and sizes the tiled kernel of
+// moe_grouped.cu does not take).
+//
+// Choice (one warp per token, all 32-bit): s_e = sigmoid(z_e).  The experts form n_groups equal groups of
+// neighbours; a group's mark is the sum of its two largest s (of its one, if it has one expert); only experts of
+// the `keep` groups with the largest marks can be chosen; of those the `top` with the largest s are, and their
+// weights are s / (sum of the chosen s + 1e-20) * scale.  Equal values: the lower index wins.
+#include <math.h>
+
+#include "common.cuh"
+
+constexpr int MOE_MAX_EXPERTS = 1024;
+constexpr int MOE_MAX_TOP = 32;
+
+__global__ void __launch_bounds__(32) moe_route_kernel(const float* __restrict__ z, int E, int n_groups, int keep, int top,
+                                                       float scale, int* __restrict__ ids, float* __restrict__ weights) {
+    __shared__ float s[MOE_MAX_EXPERTS];
+    __shared__ float mark[MOE_MAX_EXPERTS];
+    __shared__ unsigned char open_[MOE_MAX_EXPERTS];        // 1: the expert may still be chosen
+    __shared__ int chosen[MOE_MAX_TOP];
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const int size = E / n_groups;
+    for (int e = lane; e < E; e += 32) {
+        s[e] = 1.f / (1.f + expf(-z[size_t(t) * E + e]));
+        open_[e] = 0;
+    }
+    __syncwarp();
+    for (int g = lane; g < n_groups; g += 32) {
+        float a = -1.f, b = -1.f;                           // the two largest (scores are positive)
+        for (int i = 0; i < size; ++i) {
+            const float v = s[g * size + i];
+            if (v > a) { b = a; a = v; }
+            else if (v > b) b = v;
+        }
+        mark[g] = a + (b > 0.f ? b : 0.f);
+    }
+    __syncwarp();
+    for (int r = 0; r < keep; ++r) {                        // the group with the largest mark, `keep` times
+        float best = -1.f;
+        int arg = 0x7fffffff;
+        for (int g = lane; g < n_groups; g += 32)
+            if (mark[g] > best) { best = mark[g]; arg = g; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg != 0x7fffffff) {
+            for (int i = lane; i < size; i += 32) open_[arg * size + i] = 1;
+            if (lane == 0) mark[arg] = -2.f;
+        }
+        __syncwarp();
+    }
+    float sum = 0.f;
+    for (int r = 0; r < top; ++r) {
+        float best = -1.f;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (open_[e] && s[e] > best) { best = s[e]; arg = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0) {
+            chosen[r] = arg == 0x7fffffff ? 0 : arg;
+            if (arg != 0x7fffffff) open_[arg] = 0;
+        }
+        sum += arg == 0x7fffffff ? 0.f : best;
+        __syncwarp();
+    }
+    for (int r = lane; r < top; r += 32) {
+        ids[size_t(t) * top + r] = chosen[r];
+        weights[size_t(t) * top + r] = s[chosen[r]] / (sum + 1e-20f) * scale;
+    }
+}
+
+// z float32 [T, E] router logits -> ids int32 [T, top], weights float32 [T, top], largest score first.
+GB_API int gb_moe_route(const float* z, int T, int E, int n_groups, int keep, int top, float scale, int* ids, float* weights,
+                        cudaStream_t stream) {
+    GB_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS, "gb_moe_route: %d experts (1..%d)", E, MOE_MAX_EXPERTS);
+    GB_REQUIRE(n_groups > 0 && E % n_groups == 0 && keep > 0 && keep <= n_groups, "gb_moe_route: %d experts in %d groups, %d kept", E, n_groups, keep);
+    GB_REQUIRE(top > 0 && top <= MOE_MAX_TOP && top <= keep * (E / n_groups), "gb_moe_route: %d experts cannot be chosen from %d groups of %d (at most %d)", top, keep, E / n_groups, MOE_MAX_TOP);
+    if (T == 0) return 0;
+    moe_route_kernel<<<T, 32, 0, stream>>>(z, E, n_groups, keep, top, scale, ids, weights);
+    GB_LAUNCH_OK("gb_moe_route");
+    return 0;
+}
+
+// ---------------------------------------------------------------- experts, token by token
+// y[t, r, f] = unit(Wg[e] h_t, Wu[e] h_t)_f with e = ids[t, r]; unit = gb_act_glu_clamped.  One block per (token,
+// choice) and slice of 32 features; the token's row lies in shared memory as 32-bit floats, a warp takes a feature at a
+// time and its lanes share the two matrix rows in pieces of eight (bfloat16) or four (float32) entries.
+template <typename TW>
+__device__ __forceinline__ float moe_row_dot(const TW* __restrict__ w, const float* __restrict__ hs, int K, int lane);
+
+template <>
+__device__ __forceinline__ float moe_row_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ hs, int K, int lane) {
+    float acc = 0.f;
+    if (K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        for (int i = lane * 8; i < K; i += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 v = __bfloat1622float2(p2[e]);
+                acc = fmaf(v.x, hs[i + 2 * e], acc);
+                acc = fmaf(v.y, hs[i + 2 * e + 1], acc);
+            }
+        }
+    } else {
+        for (int i = lane; i < K; i += 32) acc = fmaf(__bfloat162float(w[i]), hs[i], acc);
+    }
+    return gb_warp_sum(acc);
+}
+template <>
+__device__ __forceinline__ float moe_row_dot<float>(const float* __restrict__ w, const float* __restrict__ hs, int K, int lane) {
+    float acc = 0.f;
+    if (K % 4 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        for (int i = lane * 4; i < K; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(w + i);
+            acc = fmaf(v.x, hs[i], acc);
+            acc = fmaf(v.y, hs[i + 1], acc);
+            acc = fmaf(v.z, hs[i + 2], acc);
+            acc = fmaf(v.w, hs[i + 3], acc);
+        }
+    } else {
+        for (int i = lane; i < K; i += 32) acc = fmaf(w[i], hs[i], acc);
+    }
+    return gb_warp_sum(acc);
+}
+
+constexpr int MOE_SLICE = 32;
+
+template <typename TW>
+__global__ void __launch_bounds__(128) moe_gate_up_kernel(const void* __restrict__ h, int h_dtype, long long ldh, int K, int F,
+                                                          int top, const int* __restrict__ ids, const TW* __restrict__ wg,
+                                                          const TW* __restrict__ wu, float limit, void* __restrict__ y,
+                                                          int y_dtype) {
+    extern __shared__ float moe_hs[];
+    const int pair = blockIdx.x, t = pair / top;
+    const int e = ids[pair];
+    for (int i = threadIdx.x; i < K; i += blockDim.x) moe_hs[i] = gb_load(h, h_dtype, size_t(t) * ldh + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f_end = min(F, (blockIdx.y + 1) * MOE_SLICE);
+    for (int f = blockIdx.y * MOE_SLICE + warp; f < f_end; f += 4) {
+        const size_t row = (size_t(e) * F + f) * K;
+        const float g = moe_row_dot<TW>(wg + row, moe_hs, K, lane);
+        const float u = moe_row_dot<TW>(wu + row, moe_hs, K, lane);
+        if (lane == 0) gb_store(y, y_dtype, size_t(pair) * F + f, gb_act_glu_clamped(g, u, limit));
+    }
+}
+
+// out[t, n] (+)= sum_r weights[t, r] sum_f Wd[ids[t, r]][n, f] y[t, r, f].  One block per token and slice of 32
+// results; the token's top * F unit outputs lie in shared memory, already multiplied by their weights.
+template <typename TW>
+__global__ void __launch_bounds__(128) moe_down_kernel(const void* __restrict__ y, int y_dtype, int F, int N, int top,
+                                                       const int* __restrict__ ids, const float* __restrict__ weights,
+                                                       const TW* __restrict__ wd, float* __restrict__ out, int accumulate) {
+    extern __shared__ float moe_ys[];
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < top * F; i += blockDim.x)
+        moe_ys[i] = gb_load(y, y_dtype, size_t(t) * top * F + i) * weights[size_t(t) * top + i / F];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_end = min(N, (blockIdx.y + 1) * MOE_SLICE);
+    for (int n = blockIdx.y * MOE_SLICE + warp; n < n_end; n += 4) {
+        float acc = 0.f;
+        for (int r = 0; r < top; ++r) {
+            const int e = ids[size_t(t) * top + r];
+            acc += moe_row_dot<TW>(wd + (size_t(e) * N + n) * F, moe_ys + r * F, F, lane);
+        }
+        if (lane == 0) out[size_t(t) * N + n] = accumulate ? out[size_t(t) * N + n] + acc : acc;
+    }
+}
+
+static int moe_smem(const void* kernel, size_t bytes, const char* what) {
+    if (bytes <= 48 * 1024) return 0;
+    if (bytes > 200 * 1024) return gb_fail("%s: rows of %zu bytes do not fit shared memory", what, bytes);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess)
+        return gb_fail("%s: cannot get %zu bytes of shared memory", what, bytes);
+    return 0;
+}
+
+// h [T, K] rows ldh apart; ids [T, top]; wg, wu [E, F, K] contiguous (dtype w_dtype); y [T, top, F] contiguous.
+GB_API int gb_moe_gate_up(const void* h, int h_dtype, long long ldh, int T, int K, int F, int top, const int* ids,
+                          const void* wg, const void* wu, int w_dtype, float limit, void* y, int y_dtype, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(h_dtype) && gb_is_dtype(w_dtype) && gb_is_dtype(y_dtype), "gb_moe_gate_up: bad dtype");
+    GB_REQUIRE(K > 0 && F > 0 && top > 0 && limit > 0.f, "gb_moe_gate_up: bad sizes K=%d F=%d top=%d limit=%g", K, F, top, limit);
+    if (T == 0) return 0;
+    const size_t smem = size_t(K) * 4;
+    dim3 grid(T * top, (F + MOE_SLICE - 1) / MOE_SLICE);
+    GB_REQUIRE(grid.y <= 65535, "gb_moe_gate_up: an expert of %d hidden entries is too wide", F);
+    if (w_dtype == GB_F32) {
+        if (moe_smem((const void*)moe_gate_up_kernel<float>, smem, "gb_moe_gate_up")) return 1;
+        moe_gate_up_kernel<float><<<grid, 128, smem, stream>>>(h, h_dtype, ldh, K, F, top, ids, (const float*)wg, (const float*)wu, limit, y, y_dtype);
+    } else {
+        if (moe_smem((const void*)moe_gate_up_kernel<__nv_bfloat16>, smem, "gb_moe_gate_up")) return 1;
+        moe_gate_up_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(h, h_dtype, ldh, K, F, top, ids, (const __nv_bfloat16*)wg,
+                                                                        (const __nv_bfloat16*)wu, limit, y, y_dtype);
+    }
+    GB_LAUNCH_OK("gb_moe_gate_up");
+    return 0;
+}
+
+// y [T, top, F]; wd [E, N, F] contiguous; out float32 [T, N] contiguous (added to when accumulate).
+GB_API int gb_moe_down(const void* y, int y_dtype, int T, int F, int N, int top, const int* ids, const float* weights,
+                       const void* wd, int w_dtype, float* out, int accumulate, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(y_dtype) && gb_is_dtype(w_dtype), "gb_moe_down: bad dtype");
+    GB_REQUIRE(F > 0 && N > 0 && top > 0, "gb_moe_down: bad sizes F=%d N=%d top=%d", F, N, top);
+    if (T == 0) return 0;
+    const size_t smem = size_t(top) * F * 4;
+    dim3 grid(T, (N + MOE_SLICE - 1) / MOE_SLICE);
+    GB_REQUIRE(grid.y <= 65535, "gb_moe_down: rows of %d entries are too wide", N);
+    if (w_dtype == GB_F32) {
+        if (moe_smem((const void*)moe_down_kernel<float>, smem, "gb_moe_down")) return 1;
+        moe_down_kernel<float><<<grid, 128, smem, stream>>>(y, y_dtype, F, N, top, ids, weights, (const float*)wd, out, accumulate);
+    } else {
+        if (moe_smem((const void*)moe_down_kernel<__nv_bfloat16>, smem, "gb_moe_down")) return 1;
+        moe_down_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(y, y_dtype, F, N, top, ids, weights, (const __nv_bfloat16*)wd, out, accumulate);
+    }
+    GB_LAUNCH_OK("gb_moe_down");
+    return 0;
+}
+
+// ---------------------------------------------------------------- activations of whole buffers
+__global__ void unary_act_kernel(void* __restrict__ x, int dtype, long long n, int act) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i < n) gb_store(x, dtype, size_t(i), gb_act_unary(gb_load(x, dtype, size_t(i)), act));
+}
+
+// x <- act(x) entry by entry, in place (contiguous).  act: GbGateAct or GbUnaryAct.
+GB_API int gb_unary_act(void* x, int dtype, long long n, int act, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && act >= 1 && act <= 3, "gb_unary_act: bad dtype or activation %d", act);
+    if (n == 0) return 0;
+    unary_act_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(x, dtype, n, act);
+    GB_LAUNCH_OK("gb_unary_act");
+    return 0;
+}
+
+__global__ void glu_clamped_kernel(const void* __restrict__ gu, long long ld, void* __restrict__ out, int T, int F, int dtype,
+                                   float limit) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= (long long)T * F) return;
+    const long long t = i / F;
+    const int f = int(i - t * F);
+    gb_store(out, dtype, size_t(i), gb_act_glu_clamped(gb_load(gu, dtype, size_t(t) * ld + f), gb_load(gu, dtype, size_t(t) * ld + F + f), limit));
+}
+
+// gate_up [T, 2F] (gate in the first F columns, rows ld apart) -> out [T, F] contiguous = gb_act_glu_clamped(gate, up).
+GB_API int gb_glu_clamped(const void* gate_up, long long ld, void* out, int T, int F, int dtype, float limit, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(dtype) && F > 0 && limit > 0.f, "gb_glu_clamped: bad arguments");
+    if (T == 0) return 0;
+    const long long n = (long long)T * F;
+    glu_clamped_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(gate_up, ld, out, T, F, dtype, limit);
+    GB_LAUNCH_OK("gb_glu_clamped");
+    return 0;
+}

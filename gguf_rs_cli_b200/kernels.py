@@ -78,10 +78,15 @@ def rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.
 def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
                       kcache: torch.Tensor, vcache: Optional[torch.Tensor], window: int, scale: float,
-                      v_dim: Optional[int] = None) -> torch.Tensor:
+                      v_dim: Optional[int] = None, keep_first: int = 0, head_pages: int = 0,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """v_dim: entries of a value when they differ from a key's head_dim.  vcache None: the values are the
-    first v_dim entries of the key rows themselves (one latent row per position serves as key and value)."""
-    _cuda(q, out, seq_of, pos, table, kcache, vcache)
+    first v_dim entries of the key rows themselves (one latent row per position serves as key and value).
+    keep_first: with a window, the sequence's first positions that stay visible behind it; their pages are the first
+    head_pages entries of the page table, in front of the ring.  gate [T, heads*v_dim]: the result is multiplied by
+    sigmoid(gate)."""
+    _cuda(q, out, seq_of, pos, table, kcache, vcache, gate)
+    assert gate is None or (gate.stride(1) == 1 and gate.shape == out.shape)
     T = q.shape[0]
     v_dim = head_dim if v_dim is None else int(v_dim)
     v_row = head_dim if vcache is None else vcache.shape[-1]
@@ -90,7 +95,8 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
     call("gb_attention_generic", ptr(q), dtype_code(q), q.stride(0), ptr(out), dtype_code(out), out.stride(0), T,
          n_heads, n_kv_heads, head_dim, v_dim, v_row, ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages,
          ptr(kcache), ptr(kcache if vcache is None else vcache), dtype_code(kcache), int(window or 0), float(scale),
-         stream_ptr())
+         int(head_pages), int(keep_first or 0), ptr(gate), 0 if gate is None else dtype_code(gate),
+         0 if gate is None else gate.stride(0), stream_ptr())
     return out
 
 
@@ -176,15 +182,139 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
     return out
 
 
+HEAD_GATES = {"sigmoid": 0, "silu": 1}
+
+
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                    n_heads: int, vdim: int) -> torch.Tensor:
-    """out[t,h,:] = o[t,h,:] / sqrt(mean(o[t,h,:]^2) + eps) * weight * sigmoid(gate[t,h,:]); o float32."""
+                    n_heads: int, vdim: int, gate_function: str = "sigmoid") -> torch.Tensor:
+    """out[t,h,:] = o[t,h,:] / sqrt(mean(o[t,h,:]^2) + eps) * weight * f(gate[t,h,:]); o float32; f the sigmoid or SiLU."""
     _cuda(o, gate, weight, out)
     T = o.shape[0]
     assert o.dtype == torch.float32 and o.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
     assert o.shape == gate.shape == out.shape == (T, n_heads * vdim) and weight.numel() == vdim
     call("gb_gated_head_norm", ptr(o), o.stride(0), ptr(gate), dtype_code(gate), gate.stride(0), ptr(weight),
-         dtype_code(weight), float(eps), ptr(out), dtype_code(out), out.stride(0), T, n_heads, vdim, stream_ptr())
+         dtype_code(weight), float(eps), ptr(out), dtype_code(out), out.stride(0), T, n_heads, vdim,
+         HEAD_GATES[gate_function], stream_ptr())
+    return out
+
+
+def gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, bias: torch.Tensor, tau: float, q_scale: float,
+        state: torch.Tensor, out: torch.Tensor, ctx, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Gated linear attention over this step's tokens, from and into state [slots, heads, dim, vdim] (float32):
+    S <- diag(alpha) S + k v^T, out = S^T (q q_scale), alpha = sigmoid(a + bias)^(1/tau) per head and key channel.
+    q, k [T, heads*dim] and v [T, heads*vdim] are column slices of one buffer; a [T, heads*dim] is the decay's
+    projection; out float32 [T, heads*vdim].  Two launches: what does not depend on the state for all tokens at
+    once (into a workspace buffer), then the walk."""
+    _cuda(q, k, v, a, bias, state, out)
+    T, ld = q.shape[0], q.stride(0)
+    assert k.stride(0) == ld and v.stride(0) == ld and q.dtype == k.dtype == v.dtype
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and a.stride(1) == 1
+    assert q.shape[1] == n_heads * dim and v.shape[1] == n_heads * vdim and a.shape == (T, n_heads * dim)
+    assert state.dtype == torch.float32 and state.shape[1:] == (n_heads, dim, vdim) and state.is_contiguous()
+    assert out.dtype == torch.float32 and out.shape == (T, n_heads * vdim) and out.stride(1) == 1
+    assert bias.numel() == n_heads * dim and bias.is_contiguous() and tau > 0
+    need = native.library().gb_gla_scratch_floats(T, n_heads, dim, vdim)
+    scratch = ctx.ws.get("gla.prepared", (need,), torch.float32)
+    call("gb_gla", ptr(q), ptr(k), ptr(v), dtype_code(q), ld, ptr(a), dtype_code(a), a.stride(0), ptr(bias), dtype_code(bias),
+         1.0 / float(tau), float(q_scale), ptr(state), ptr(out), out.stride(0), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens),
+         T, ctx.B, n_heads, dim, vdim, ptr(scratch), stream_ptr())
+    return out
+
+
+def norm_residual_add(x: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                      xb: Optional[torch.Tensor] = None) -> None:
+    """x += y / sqrt(mean(y^2) + eps) * weight row by row (x float32, the sum in 32-bit); xb, when given, receives
+    bfloat16(x).  y None: only the copy is made."""
+    _cuda(x, y, weight, xb)
+    T, E = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and (y is not None or xb is not None)
+    assert y is None or (y.shape == (T, E) and y.stride(1) == 1 and weight.numel() == E)
+    assert xb is None or (xb.dtype == torch.bfloat16 and xb.shape == (T, E) and xb.is_contiguous())
+    call("gb_norm_residual_add", ptr(x), ptr(y), 0 if y is None else dtype_code(y), 0 if y is None else y.stride(0), T, E,
+         ptr(weight), 0 if weight is None else dtype_code(weight), float(eps), ptr(xb), stream_ptr())
+
+
+def head_prep_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       inv_freq: Optional[torch.Tensor], rotary_dim: int, pairing: int, v_first: Optional[torch.Tensor],
+                       mix: float, first_out: Optional[torch.Tensor], seq_of: torch.Tensor, pos: torch.Tensor,
+                       table: torch.Tensor, ring_pages: int, head_pages: int, kcache: torch.Tensor, vcache: torch.Tensor) -> None:
+    """q, k, v: column slices of one row-major buffer.  Per head: RMS norm with a weight of `dim` entries that all
+    heads share (q_weight, k_weight; None: no norm), then the rotation of the first rotary_dim entries (inv_freq None:
+    none); q in place, k into the cache.  v <- (1 - mix) v + mix v_first when v_first [T, kv_heads*vdim] is given,
+    into the cache; first_out receives v as it came."""
+    _cuda(q, k, v, q_weight, k_weight, inv_freq, v_first, first_out, seq_of, pos, table, kcache, vcache)
+    T, ld = q.shape[0], q.stride(0)
+    assert q.stride(1) == 1 and k.stride(0) == ld and v.stride(0) == ld and k.dtype == q.dtype == v.dtype
+    assert kcache.shape[-1] == dim and vcache.shape[-1] == vdim and kcache.dtype == vcache.dtype
+    assert (q_weight is None) == (k_weight is None) and (q_weight is None or (q_weight.numel() == dim == k_weight.numel() and q_weight.dtype == k_weight.dtype))
+    for t in (v_first, first_out):
+        assert t is None or (t.shape == (T, n_kv_heads * vdim) and t.stride(1) == 1 and t.dtype == q.dtype)
+    call("gb_head_prep_kv_write", ptr(q), ptr(k), ptr(v), dtype_code(q), ld, T, n_heads, n_kv_heads, dim, vdim, ptr(q_weight),
+         ptr(k_weight), 0 if q_weight is None else dtype_code(q_weight), float(eps), ptr(inv_freq), int(rotary_dim), int(pairing),
+         ptr(v_first), 0 if v_first is None else v_first.stride(0), float(mix), ptr(first_out),
+         0 if first_out is None else first_out.stride(0), ptr(seq_of), ptr(pos), ptr(table), table.shape[1], int(ring_pages),
+         int(head_pages), ptr(kcache), ptr(vcache), dtype_code(kcache), stream_ptr())
+
+
+def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, scale: float, ids: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    """Router logits float32 [T, experts] -> ids int32 [T, top] and weights float32 [T, top]: scores are sigmoids; the
+    experts form n_groups equal groups of neighbours, a group's mark is the sum of its two largest scores, only the
+    `keep` best groups' experts can be chosen; weights are the chosen scores over their sum, times scale."""
+    _cuda(logits, ids, weights)
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    assert ids.shape == (T, top) and weights.shape == (T, top) and ids.is_contiguous() and weights.is_contiguous()
+    call("gb_moe_route", ptr(logits), T, E, int(n_groups), int(keep), int(top), float(scale), ptr(ids), ptr(weights), stream_ptr())
+
+
+def moe_gate_up(h: torch.Tensor, ids: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, limit: float,
+                y: torch.Tensor) -> torch.Tensor:
+    """y[t, r, :] = unit(W_gate[e] h_t, W_up[e] h_t), e = ids[t, r]; unit(g, u) = g' sigmoid(1.702 g') (u' + 1) with
+    g' = min(g, limit), u' = clamp(u, -limit, limit).  w_gate, w_up [experts, F, K]; token by token on the CUDA cores."""
+    _cuda(h, ids, w_gate, w_up, y)
+    T, K = h.shape
+    E, F, _ = w_gate.shape
+    top = ids.shape[1]
+    assert h.stride(1) == 1 and w_gate.is_contiguous() and w_up.is_contiguous() and w_gate.shape == w_up.shape == (E, F, K)
+    assert w_gate.dtype == w_up.dtype and y.shape == (T, top, F) and y.is_contiguous() and ids.is_contiguous()
+    call("gb_moe_gate_up", ptr(h), dtype_code(h), h.stride(0), T, K, F, top, ptr(ids), ptr(w_gate), ptr(w_up), dtype_code(w_gate),
+         float(limit), ptr(y), dtype_code(y), stream_ptr())
+    return y
+
+
+def moe_down(y: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor,
+             accumulate: bool = False) -> torch.Tensor:
+    """out[t] (+)= sum_r weights[t, r] W_down[ids[t, r]] y[t, r]; w_down [experts, N, F]; out float32 [T, N]."""
+    _cuda(y, ids, weights, w_down, out)
+    T, top, F = y.shape
+    E, N, _ = w_down.shape
+    assert y.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, N, F) and out.shape == (T, N)
+    assert out.dtype == torch.float32 and out.is_contiguous() and ids.shape == (T, top) and weights.shape == (T, top)
+    call("gb_moe_down", ptr(y), dtype_code(y), T, F, N, top, ptr(ids), ptr(weights), ptr(w_down), dtype_code(w_down), ptr(out),
+         int(bool(accumulate)), stream_ptr())
+    return out
+
+
+UNARY_ACTS = {"silu": 1, "gelu_tanh": 2, "gelu": 3}
+
+
+def unary_act_(x: torch.Tensor, activation: str) -> torch.Tensor:
+    """x <- act(x) in place; gelu is the exact form 0.5 z (1 + erf(z / sqrt 2))."""
+    _cuda(x)
+    assert x.is_contiguous()
+    call("gb_unary_act", ptr(x), dtype_code(x), x.numel(), UNARY_ACTS[activation], stream_ptr())
+    return x
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float) -> torch.Tensor:
+    """gate_up [T, 2F], gate in the first F columns; out[t, i] = g' sigmoid(1.702 g') (u' + 1) with the inputs clamped
+    as in moe_gate_up."""
+    _cuda(gate_up, out)
+    T, F = out.shape
+    assert gate_up.shape == (T, 2 * F) and gate_up.stride(1) == 1 and out.is_contiguous() and out.dtype == gate_up.dtype
+    call("gb_glu_clamped", ptr(gate_up), gate_up.stride(0), ptr(out), T, F, dtype_code(out), float(limit), stream_ptr())
     return out
 
 

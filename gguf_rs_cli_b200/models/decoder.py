@@ -154,7 +154,7 @@ class Decoder:
                 gi, i = cache.group_of_run[src]
                 g = cache.groups[gi]
                 views.append(RunView(r, run.layer, run.cache_of is None, gi, g.k[i], None if g.v is None else g.v[i], g.ring_pages,
-                                      g.spec))
+                                      g.spec, g.head_pages))
             else:
                 views.append(RunView(r, run.layer, False))
         return views

@@ -140,13 +140,23 @@ _SIGNATURES = {
     "gb_swiglu": [_P, _L, _P, _I, _I, _I, _I, _P],
     "gb_zero_rows": [_P, _P, _I, _I, _P],
     "gb_gemm_generic": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P],
-    "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _P],
+    "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _I, _I, _P, _I, _L, _P],
     "gb_add_dyt": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P],
     "gb_scale": [_P, _L, _F, _P],
     "gb_short_conv_silu": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _L, _P],
     "gb_delta_rule": [_P, _P, _P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "gb_delta_rule_scratch_floats": [_I, _I, _I, _I, _I],
-    "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _P],
+    "gb_gated_head_norm": [_P, _L, _P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _I, _I, _P],
+    "gb_norm_residual_add": [_P, _P, _I, _L, _I, _I, _P, _I, _F, _P, _P],
+    "gb_head_prep_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P, _L, _F, _P, _L, _P, _P, _P,
+                              _I, _I, _I, _P, _P, _I, _P],
+    "gb_gla": [_P, _P, _P, _I, _L, _P, _I, _L, _P, _I, _F, _F, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "gb_gla_scratch_floats": [_I, _I, _I, _I],
+    "gb_moe_route": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
+    "gb_moe_gate_up": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _I, _P],
+    "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P],
+    "gb_unary_act": [_P, _I, _L, _I, _P],
+    "gb_glu_clamped": [_P, _L, _P, _I, _I, _I, _F, _P],
     "gb_qk_norm_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P],
     "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _P],
     "gb_pack_latent_heads": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P],
@@ -186,7 +196,7 @@ _SIGNATURES = {
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }
-_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
+_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:
@@ -222,7 +232,7 @@ def library():
 
 _launches = 0
 # kernels launched by one call of an entry point, where that is not one
-KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2}
+KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2, "gb_gla": 2}
 
 
 def launch_count() -> int:

@@ -13,6 +13,14 @@ rotation: values of another size than keys (`v_head_dim`); queries and keys divi
 root mean square per head, without a weight (`qk_norm_eps`); and a query temperature that grows
 with the position, q <- q (1 + coef ln(floor((p + 1) / every) + 1)) (`q_temp`).  With any of them
 scores, softmax and the mix of values run in 32-bit in the general attention kernel.
+
+Further options, for designs that norm and gate their heads (they go with a rotation, and also keep scores and
+weights in 32-bit): an RMS norm per head on q and k with a weight of head_dim entries that all heads share, before
+the rotation (`head_norm_eps`); the first positions of a sequence that stay visible behind the window
+(`keep_first`; the cache keeps their pages in front of its ring); the heads' results multiplied by
+sigmoid(W_g h) before the output projection (`out_gate`); and values mixed across layers (`v_mix`): the first
+layer that says so ("gives") leaves its values of the step's tokens for the later ones ("takes"), which cache
+v <- (1 - lambda) v + lambda v_first with a scalar lambda of their own.
 """
 from __future__ import annotations
 
@@ -32,8 +40,11 @@ from .registry import register_mixer
 class Attention(Part):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window (None or W),
     bias (q/k/v biases), shares_kv (default False), v_head_dim (default head_dim),
-    qk_norm_eps (default None: no normalisation), q_temp (default None, or {"coef", "every"}).
-    tensors: q [nh*hd, E], k [nkv*hd, E], v [nkv*vd, E], o [E, nh*vd], optional q_bias, k_bias, v_bias."""
+    qk_norm_eps (default None: no normalisation), q_temp (default None, or {"coef", "every"}),
+    head_norm_eps (default None), keep_first (default 0), out_gate (default False), v_mix (None, "gives" or "takes"),
+    v_mix_optional (the folder may hold the scalar although nothing is mixed).
+    tensors: q [nh*hd, E], k [nkv*hd, E], v [nkv*vd, E], o [E, nh*vd], optional q_bias, k_bias, v_bias;
+    with head_norm_eps q_norm, k_norm [hd]; with out_gate g [nh*vd, E]; with v_mix the scalar v_mix."""
 
     def __init__(self, spec, dtype, device, position=None):
         super().__init__(spec, dtype, device)
@@ -51,9 +62,21 @@ class Attention(Part):
         self.temp_coef, self.temp_every = (float(temp["coef"]), int(temp["every"])) if temp else (0.0, 1)
         if temp and self.temp_every <= 0:
             raise ValueError(f"attention: q_temp.every must be a positive whole number, got {temp['every']!r}")
+        self.head_norm_eps = p.get("head_norm_eps")
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.out_gate = bool(p.get("out_gate", False))
+        self.v_mix = p.get("v_mix") or None
+        if self.v_mix not in (None, "gives", "takes"):
+            raise ValueError(f"attention: v_mix {self.v_mix!r} is not one of None, 'gives', 'takes'")
+        # heads with a norm of their own, a gate, kept first positions or mixed values: prepared by one kernel
+        # (norm, rotation, mixing, cache write) and attended to with 32-bit weights
+        self.prepared = bool(self.head_norm_eps is not None or self.keep_first or self.out_gate or self.v_mix)
         # normalised q and k, a query temperature or values of their own size: the exact path
-        self.exact = self.vd != self.hd or self.qk_norm_eps is not None or self.temp_coef != 0.0
-        if self.exact and (position is not None or self.shares_kv):
+        self.exact = self.prepared or self.vd != self.hd or self.qk_norm_eps is not None or self.temp_coef != 0.0
+        if self.prepared and (self.qk_norm_eps is not None or self.temp_coef != 0.0 or self.shares_kv or p.get("bias")):
+            raise ValueError("attention: head_norm_eps, keep_first, out_gate and v_mix go with none of qk_norm_eps, q_temp, "
+                             "shares_kv and biases")
+        if self.exact and not self.prepared and (position is not None or self.shares_kv):
             raise ValueError("attention: qk_norm_eps, q_temp and v_head_dim go with neither a rotation nor shares_kv")
 
     def kv_spec(self) -> Optional[KVSpec]:
@@ -61,7 +84,7 @@ class Attention(Part):
 
     def reads_kv_spec(self) -> KVSpec:
         """The kind of cache this mixer can read (its own, or another run's)."""
-        return KVSpec(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd)
+        return KVSpec(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd, self.keep_first)
 
     def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         return {}
@@ -74,11 +97,19 @@ class Attention(Part):
         req.append(TensorRequest(t["o"], (E, self.nh * self.vd)))
         if self.p.get("bias"):
             req += [TensorRequest(t[n + "_bias"], (rows[n],)) for n in names]
+        if self.head_norm_eps is not None:
+            req += [TensorRequest(t["q_norm"], (self.hd,), init="ones"), TensorRequest(t["k_norm"], (self.hd,), init="ones")]
+        if self.out_gate:
+            req.append(TensorRequest(t["g"], (self.nh * self.vd, E)))
+        if self.v_mix or self.p.get("v_mix_optional"):
+            req.append(TensorRequest(t["v_mix"], (), optional=not self.v_mix, init="const:0.25" if self.v_mix else None))
         return req
 
     def load(self, store: WeightStore) -> None:
         req = {r.name: r for r in self.tensor_requests()}
         t = self.spec.tensors
+        if self.prepared:
+            return self._load_prepared(store, req)
         names = ["q"] + ([] if self.shares_kv else ["k", "v"])
         mats = [store.get(req[t[n]]) for n in names]
         dt = mats[0].dtype
@@ -89,15 +120,45 @@ class Attention(Part):
         self.qkv = Linear(w, b, name="attn.qkv")
         self.o = Linear(store.get(req[t["o"]]), name="attn.o")
 
+    def _load_prepared(self, store: WeightStore, req) -> None:
+        """q, k, v and the gate as one matrix, each part starting at a multiple of 8 rows (zero rows between), so that
+        one product reads h once and every slice of its result is aligned."""
+        t = self.spec.tensors
+        names = ["q", "k", "v"] + (["g"] if self.out_gate else [])
+        mats = [store.get(req[t[n]]) for n in names]
+        dt = mats[0].dtype
+        parts, self.off, rows = [], {}, 0
+        for n, m in zip(names, mats):
+            pad = (rows + 7) // 8 * 8 - rows
+            if pad:
+                parts.append(torch.zeros(pad, m.shape[1], dtype=dt, device=m.device))
+            self.off[n] = rows + pad
+            parts.append(m.to(dt))
+            rows = self.off[n] + m.shape[0]
+        pad = (rows + 7) // 8 * 8 - rows
+        if pad:
+            parts.append(torch.zeros(pad, mats[0].shape[1], dtype=dt, device=mats[0].device))
+        self.qkv = Linear(torch.cat(parts, dim=0).contiguous(), name="attn.qkvg")
+        self.o = Linear(store.get(req[t["o"]]), name="attn.o")
+        self.q_norm = self.k_norm = None
+        if self.head_norm_eps is not None:
+            self.q_norm, self.k_norm = store.get(req[t["q_norm"]]), store.get(req[t["k_norm"]])
+            if self.q_norm.dtype != self.k_norm.dtype:
+                self.k_norm = self.k_norm.to(self.q_norm.dtype)
+        self.mix = 0.0
+        if self.v_mix == "takes":
+            lam = store.get(req[t["v_mix"]])
+            self.mix = float(lam.float().item()) if lam.device.type != "meta" else 0.0
+
     accepts_residual = True
 
     # ---- planning on the host
     def plan_key(self):
-        return ("attention", self.hd, self.window, self.exact)
+        return ("attention", self.hd, self.window, self.exact, self.prepared, self.keep_first)
 
     def plan(self, batch: HostBatch):
         """Prompts: the list of query tiles (sequence row, first query) that the prefill kernel's CTAs take."""
-        if batch.decode or (self.exact and not self._exact_tiled()):
+        if batch.decode or self.prepared or (self.exact and not self._exact_tiled()):
             return {}
         return {"tiles": kernels.attention_prefill_tiles(batch.qlens)}
 
@@ -114,6 +175,8 @@ class Attention(Part):
     def graph_class(self, batch: HostBatch):
         """The decode kernel splits each sequence's pages over CTAs by a rule of the longest sequence; steps
         of one class launch the same grid and may share a captured graph."""
+        if self.prepared:
+            return ()                     # the general kernel: one block per token and head, whatever the lengths
         if self.exact:
             # the general kernel: one block per token and head, whatever the lengths; the CUDA-core decode kernel
             # splits each sequence's pages by a rule of the longest sequence
@@ -129,8 +192,45 @@ class Attention(Part):
         self.qkv.fold_input_scale(weight)
         return True
 
+    V_FIRST = "attention.v_first"          # where the layer that gives its values leaves them for the step's later layers
+
+    def _forward_prepared(self, h, ctx: StepContext, run: RunView) -> torch.Tensor:
+        """One product for q, k, v and the gate; one kernel for the heads' norm, the rotation, the mixing of values and
+        the cache write; attention with 32-bit scores and weights behind the window and the kept first positions, its
+        result gated; the output projection in 32-bit results."""
+        nh, nkv, hd, vd, T = self.nh, self.nkv, self.hd, self.vd, h.shape[0]
+        proj = self.qkv(h, ctx)
+        ctx.mark("qkv")
+        off = self.off
+        q, k, v = (proj[:, off["q"]:off["q"] + nh * hd], proj[:, off["k"]:off["k"] + nkv * hd],
+                   proj[:, off["v"]:off["v"] + nkv * vd])
+        gate = proj[:, off["g"]:off["g"] + nh * vd] if self.out_gate else None
+        v_first = first_out = None
+        if self.v_mix == "gives":
+            first_out = ctx.shared[self.V_FIRST] = ctx.ws.get("attn.v_first", (T, nkv * vd), proj.dtype)
+        elif self.v_mix == "takes":
+            v_first = ctx.shared.get(self.V_FIRST)
+            if v_first is None or v_first.shape != (T, nkv * vd):
+                raise RuntimeError("attention: no earlier layer of this step has left values of this size to mix with")
+        table, pos = ctx.tables[run.group], self.position
+        kernels.head_prep_kv_write(q, k, v, nh, nkv, hd, vd, self.q_norm, self.k_norm, self.head_norm_eps or 1.0,
+                                   None if pos is None else pos.inv_freq, 0 if pos is None else pos.rotary_dim,
+                                   0 if pos is None else pos.pairing, v_first, self.mix, first_out, ctx.seq_of, ctx.pos, table,
+                                   run.ring_pages, run.head_pages, run.k, run.v)
+        ctx.mark("heads")
+        out = ctx.ws.get("attn.out", (T, nh * vd), ctx.dtype)
+        kernels.attention_generic(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
+                                  self.window or 0, self.scale, v_dim=vd, keep_first=self.keep_first,
+                                  head_pages=run.head_pages, gate=gate)
+        ctx.mark("attention")
+        term = self.o(out, ctx, out_dtype=torch.float32)
+        ctx.mark("o")
+        return term
+
     def forward(self, h, ctx: StepContext, run: RunView, residual=None) -> Optional[torch.Tensor]:
         nh, nkv, hd = self.nh, self.nkv, self.hd
+        if self.prepared:
+            return self._forward_prepared(h, ctx, run)
         qkv = self.qkv(h, ctx)
         ctx.mark("qkv")
         if self.exact:

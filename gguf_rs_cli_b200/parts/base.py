@@ -109,6 +109,7 @@ class RunView:
     v: Optional[torch.Tensor] = None
     ring_pages: int = 1
     kv_spec: Optional[KVSpec] = None
+    head_pages: int = 0           # table entries in front of the ring: pages of first positions that are kept for ever
 
 
 @dataclass
@@ -135,6 +136,7 @@ class StepContext:
     plans: Dict = field(default_factory=dict)   # plan key -> {name: int32 device tensor} (see plan_of)
     marks: Optional[List] = None                # (label, CUDA event) after each stage, when the step is profiled
     mark_detail: bool = True
+    shared: Dict = field(default_factory=dict)  # name -> tensor that a part leaves for later parts of the same step
 
     def state(self, name: str) -> torch.Tensor:
         """Fixed-size per-sequence state [slots, ...]; index it with ctx.slots."""

@@ -1,6 +1,9 @@
 """Arrangements of a layer's parts around the residual stream."""
 from __future__ import annotations
 
+import torch
+
+from .. import kernels
 from .base import RunView, StepContext, Stream
 from .registry import register_block
 
@@ -58,3 +61,41 @@ class PreNormBlock:
         if term is not None:
             stream.pending = term
             stream.drop_shadow()
+
+
+@register_block("outnorm")
+class OutputNormBlock:
+    """x += norm_m(mixer(x)); x += norm_f(ff(x)): the sublayers read the residual stream itself, and what they give
+    is normed on its way into it.  The sums are 32-bit; in bfloat16 mode the products read a bfloat16 copy of x that
+    the norm's kernel renews with every sum (`Stream.xb`)."""
+
+    norm_names = ("mixer", "feed_forward")
+    graph_class = ()
+
+    def __init__(self, mixer, feed_forward, norms):
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+        for name in self.norm_names:
+            if name in norms and not hasattr(norms[name], "add_normed"):
+                raise ValueError(f"outnorm: the norm of kind {norms[name].spec.kind!r} cannot norm a sublayer's result into the stream")
+
+    def forward(self, stream: Stream, ctx: StepContext, run: RunView) -> None:
+        term = self.mixer.forward(self._rows(stream, ctx), ctx, run)
+        self.norms["mixer"].add_normed(stream, term, ctx)
+        ctx.mark("mixer_norm")
+        if self.feed_forward is None:
+            return
+        term = self.feed_forward.forward(self._rows(stream, ctx), ctx)
+        self.norms["feed_forward"].add_normed(stream, term, ctx)
+        ctx.mark("ff_norm")
+
+    @staticmethod
+    def _rows(stream: Stream, ctx: StepContext):
+        """x as the sublayers' products read it: x itself in 32-bit mode, else its bfloat16 copy."""
+        if stream.pending is not None:
+            raise RuntimeError("outnorm: a term is pending on the stream; this arrangement adds every term at once")
+        if ctx.dtype == torch.float32:
+            return stream.x
+        if stream.xb is None:
+            stream.xb = ctx.ws.get("stream.xb", stream.x.shape, torch.bfloat16)
+            kernels.norm_residual_add(stream.x, None, None, 1.0, xb=stream.xb)
+        return stream.xb

@@ -70,3 +70,108 @@ class GatedMLP(Part):
         term = self.down(act, ctx, residual=residual)
         ctx.mark("down")
         return term
+
+
+@register_feed_forward("mlp")
+class PlainMLP(Part):
+    """down(act(up(h))): a feed-forward without a gate.  params: hidden_size, intermediate_size, activation ("gelu":
+    the exact form with erf; "gelu_tanh"; "silu").  tensors: up [F, E], down [E, F]."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.activation = self.p.get("activation", "gelu")
+        if self.activation not in kernels.UNARY_ACTS:
+            raise ValueError(f"mlp: activation {self.activation!r} is not supported {sorted(kernels.UNARY_ACTS)}")
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        E, F, t = self.p["hidden_size"], self.p["intermediate_size"], self.spec.tensors
+        return [TensorRequest(t["up"], (F, E)), TensorRequest(t["down"], (E, F))]
+
+    def load(self, store: WeightStore) -> None:
+        u, d = (store.get(r) for r in self.tensor_requests())
+        self.up, self.down = Linear(u, name="ff.up"), Linear(d, name="ff.down")
+
+    graph_class = ()
+
+    def forward(self, h, ctx: StepContext) -> torch.Tensor:
+        act = kernels.unary_act_(self.up(h, ctx), self.activation)
+        ctx.mark("up")
+        term = self.down(act, ctx, out_dtype=torch.float32)
+        ctx.mark("down")
+        return term
+
+
+@register_feed_forward("moe")
+class RoutedExperts(Part):
+    """A mixture of small gated feed-forwards of which each token uses a few, plus an optional one that all tokens
+    use.  An expert is down(unit(gate(h), up(h))) with unit(g, u) = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit),
+    u' = clamp(u, -limit, limit); no biases.  The router (32-bit): scores sigmoid(W_r h); the experts form `groups`
+    equal groups of neighbours, a group's mark is the sum of its two largest scores, and only experts of the `keep`
+    best groups can be chosen; the `top` largest of those are, with weights score / (sum of the chosen scores + 1e-20)
+    * scale.  The reference has no routed feed-forward (src/model/llama.rs:399-402 is its dense one).
+
+    params: hidden_size, experts, top, groups, keep, scale, expert_ff, limit, shared_ff, shared_limit (None: no shared
+    expert).  tensors: router [experts, E]; experts: the prefix of the experts' names (<prefix><i>.gate [F, E], .up
+    [F, E], .down [E, F]); shared: the prefix of the shared expert's (.gate, .up [Fs, E], .down [E, Fs])."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        p = self.p
+        self.n, self.top, self.F = int(p["experts"]), int(p["top"]), int(p["expert_ff"])
+        self.groups, self.keep = int(p.get("groups") or 1), int(p.get("keep") or 1)
+        self.shared_ff = p.get("shared_ff")
+        if self.n % self.groups or self.keep > self.groups or self.top > self.keep * (self.n // self.groups):
+            raise ValueError(f"moe: {self.top} of {self.n} experts in {self.groups} groups of which {self.keep} are kept")
+
+    def _names(self):
+        t = self.spec.tensors
+        return [(f"{t['experts']}{i}.{part}") for i in range(self.n) for part in ("gate", "up", "down")]
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        E, F, t = self.p["hidden_size"], self.F, self.spec.tensors
+        req = [TensorRequest(t["router"], (self.n, E))]
+        for name in self._names():
+            req.append(TensorRequest(name, (E, F) if name.endswith(".down") else (F, E)))
+        if self.shared_ff:
+            Fs = int(self.shared_ff)
+            req += [TensorRequest(t["shared"] + ".gate", (Fs, E)), TensorRequest(t["shared"] + ".up", (Fs, E)),
+                    TensorRequest(t["shared"] + ".down", (E, Fs))]
+        return req
+
+    def load(self, store: WeightStore) -> None:
+        req = self.tensor_requests()
+        self.router = Linear(store.get(req[0]), name="moe.router")
+        mats = [store.get(r) for r in req[1:1 + 3 * self.n]]
+        dt = mats[0].dtype
+        # the experts' matrices side by side: [experts, F, E] twice and [experts, E, F]
+        self.w_gate = torch.stack([m.to(dt) for m in mats[0::3]]).contiguous()
+        self.w_up = torch.stack([m.to(dt) for m in mats[1::3]]).contiguous()
+        self.w_down = torch.stack([m.to(dt) for m in mats[2::3]]).contiguous()
+        self.shared_gate_up = self.shared_down = None
+        if self.shared_ff:
+            g, u, d = (store.get(r) for r in req[1 + 3 * self.n:])
+            self.shared_gate_up = Linear(torch.cat([g, u.to(g.dtype)], dim=0), name="moe.shared_gate_up")
+            self.shared_down = Linear(d, name="moe.shared_down")
+
+    graph_class = ()              # grids depend on the number of tokens only
+
+    def forward(self, h, ctx: StepContext) -> torch.Tensor:
+        T, E, top = h.shape[0], self.p["hidden_size"], self.top
+        # the router's logits in 32-bit sums (the rows may be the bfloat16 copy of the stream)
+        logits = kernels.gemm_generic(h, self.router.weight, None, ctx.ws.get("moe.logits", (T, self.n), torch.float32))
+        ids = ctx.ws.get("moe.ids", (T, top), torch.int32)
+        weights = ctx.ws.get("moe.weights", (T, top), torch.float32)
+        kernels.moe_route(logits, self.groups, self.keep, top, float(self.p.get("scale", 1.0)), ids, weights)
+        ctx.mark("router")
+        out = ctx.ws.get("moe.out", (T, E), torch.float32)
+        if self.shared_ff:
+            Fs = int(self.shared_ff)
+            act = kernels.glu_clamped(self.shared_gate_up(h, ctx), ctx.ws.get("moe.shared_act", (T, Fs), ctx.dtype),
+                                      float(self.p["shared_limit"]))
+            self.shared_down(act, ctx, out_dtype=torch.float32, buffer="moe.out")
+            ctx.mark("shared")
+        y = ctx.ws.get("moe.units", (T, top, self.F), ctx.dtype)
+        kernels.moe_gate_up(h, ids, self.w_gate, self.w_up, float(self.p["limit"]), y)
+        kernels.moe_down(y, ids, weights, self.w_down, out, accumulate=bool(self.shared_ff))
+        ctx.mark("experts")
+        return out

@@ -53,6 +53,17 @@ class RMSNorm(Part):
         return out
 
 
+    def add_normed(self, stream: Stream, term: torch.Tensor, ctx: StepContext) -> None:
+        """x += term / sqrt(mean(term^2) + eps) * w: the norm of a sublayer's result on its way into the stream
+        (32-bit).  In bfloat16 mode the stream's bfloat16 copy is renewed by the same kernel; sums of squares of x
+        are not kept (a deferred norm in front of the next product would need them)."""
+        if stream.pending is not None:
+            raise RuntimeError("rmsnorm: a term is pending on the stream")
+        xb = ctx.ws.get("stream.xb", stream.x.shape, torch.bfloat16) if ctx.dtype == torch.bfloat16 else None
+        kernels.norm_residual_add(stream.x, term, self.weight, self.p["eps"], xb=xb)
+        stream.xb, stream.ssq, stream.ssq_parts = xb, None, 0
+
+
 @register_norm("dyt")
 class DynamicTanh(Part):
     """Dynamic tanh in a norm's place: tanh(alpha x) * weight + bias, no mean and no variance.
