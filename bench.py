@@ -4,7 +4,7 @@ one B200.  Prints one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--layers L] [--batch B] [--no-points] [--prompt-steps 128,256] [--shape 8b|1b|13b]
-                    [--design debonex [--sizes 1b,8b]]
+                    [--design debonex|dilalix [--sizes 1b,8b]]
 
 `value` is decoded tokens a second at batch 8 after 512-token prompts, timed on the
 device with CUDA events around K decode steps (each step: index arrays host to
@@ -303,12 +303,31 @@ def debonex_config(z):
             "norm": {"eps": 1e-5}, "layers": [pattern[i % 4] for i in range(z["layers"])]}
 
 
+def dilalix_config(z):
+    """Attention (window of 1,024 behind 64 kept positions, heads of z["head"]), gated linear attention twice, attention;
+    dense feed-forwards and mixtures of 16 experts (4 of them per token, from 2 of 4 groups, and a shared one) in turn.
+    A token's experts and the shared one together hold 5/4 of the dense feed-forward's weights."""
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4, "limit": 7.0}, "shared": {"ff": z["ff"] // 4, "limit": 7.0},
+           "router": {"experts": 16, "top": 4, "scale": 1.0, "groups": {"count": 4, "keep": 2}}}
+    attn = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"], "scale": z["head"] ** -0.5,
+            "v_mix": True, "mask": {"size": 1024, "keep_first": 64}, "rot": {"base": 10000.0, "dims": z["head"]}}
+    gla = {"heads": z["heads"], "dim": z["head"], "vdim": z["head"], "tau": 16.0}
+    pattern = [{"type": "attention", "mixer": attn, "mlp": dense}, {"type": "gla", "mixer": gla, "mlp": moe},
+               {"type": "gla", "mixer": gla, "mlp": dense}, {"type": "attention", "mixer": attn, "mlp": moe}]
+    return {"architecture": "Dilalix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "layers": [pattern[i % 4] for i in range(z["layers"])]}
+
+
 def llama_config(z):
     return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": z["layers"],
             "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"],
             "head_dim": z["head"], "intermediate_size": z["ff"], "vocab_size": z["vocab"], "rope_theta": 10000.0,
             "rope_scaling": None, "rms_norm_eps": 1e-5, "max_position_embeddings": CONTEXT, "tie_word_embeddings": False,
             "hidden_act": "silu"}
+
+
+DESIGN_CONFIGS = {"debonex": debonex_config, "dilalix": dilalix_config}
 
 
 def stage_times(llm, lens, starts=0, reps=3):
@@ -364,7 +383,10 @@ def run_design(args, pk):
     for name in [x for x in args.sizes.split(",") if x.strip()]:
         z = DESIGN_SIZES[name]
         row = {"config": z}
-        for arm, raw in ((args.design, debonex_config(z)), ("llama", llama_config(z))):
+        arms = [(args.design, DESIGN_CONFIGS[args.design](z))]
+        if args.design != "debonex":
+            arms.append(("debonex", debonex_config(z)))          # the closest of the other designs: a recurrent rule and attention
+        for arm, raw in arms + [("llama", llama_config(z))]:
             llm = from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
             torch.cuda.synchronize()
             cfg = {"vocab_size": z["vocab"]}
@@ -399,7 +421,7 @@ def main():
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--rep-penalty", type=float, default=1.0)
     ap.add_argument("--prompt-steps", default="", help="also time prompt steps of these many tokens, e.g. 128,256,512")
-    ap.add_argument("--design", default=None, choices=["debonex"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGN_CONFIGS),
                     help="instead of the headline line: prefill and decode of this design beside Llama at equal size")
     ap.add_argument("--sizes", default="1b,8b", help=f"layer sizes of --design: {sorted(DESIGN_SIZES)}")
     args = ap.parse_args()

@@ -90,6 +90,8 @@ class Cache:
             if spec.window is None:
                 ring, n_pages = width, self.n_pages
             else:
+                # where the table is too short for all kept pages and a ring, the ring below is all that is left of the
+                # table and never goes round
                 head = min(pages_for(spec.keep_first), width - 1) if spec.keep_first else 0
                 ring = min(width - head, pages_for(spec.window + self.max_step_tokens - 1) + 1)
                 n_pages = min(self.n_pages, self.n_slots * (head + ring))

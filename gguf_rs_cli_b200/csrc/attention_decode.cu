@@ -34,7 +34,16 @@ struct AdParams {
     long long ldq, ldo;
     int nh, nkv, hd, table_width, ring_pages, window, splits;
     float scale_log2;            // scale * log2(e)
+    int head_pages, keep_first;  // with a window: the sequence's first keep_first positions stay visible; their pages are
+                                 // the first head_pages entries of the table, in front of the ring
+    const __nv_bfloat16* gate;   // [T, nh*hd] rows ldg apart, or null: the result is multiplied by sigmoid(gate)
+    long long ldg;
 };
+
+__device__ __forceinline__ float ad_gated(const AdParams& p, int t, int h, int d, float o) {
+    if (!p.gate) return o;
+    return o / (1.f + expf(-__bfloat162float(p.gate[size_t(t) * p.ldg + size_t(h) * p.hd + d])));
+}
 
 __device__ __forceinline__ void unpack8(uint4 v, float* f) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -84,9 +93,13 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
 
     const int pos = p.pos[t];
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int first_page = lo >> GB_PAGE_SHIFT, n_pages = (pos >> GB_PAGE_SHIFT) - first_page + 1;
-    const int pg_begin = first_page + int((long long)split * n_pages / p.splits);
-    const int pg_end = first_page + int((long long)(split + 1) * n_pages / p.splits);
+    // the pages of the window, and in front of them those pages of kept first positions that the window does not reach
+    const int keep = p.window > 0 ? p.keep_first : 0;
+    const int first_page = lo >> GB_PAGE_SHIFT;
+    const int n_front = min((keep + GB_PAGE - 1) >> GB_PAGE_SHIFT, first_page);
+    const int n_pages = n_front + (pos >> GB_PAGE_SHIFT) - first_page + 1;
+    const int it_begin = int((long long)split * n_pages / p.splits);
+    const int it_end = int((long long)(split + 1) * n_pages / p.splits);
     const int* trow = p.table + size_t(b) * p.table_width;
 
     float m[GT], l[GT], acc[GT][HC][2];
@@ -100,12 +113,13 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
     const int key_in_warp = lane >> 1, half = lane & 1;
     const int chunks = hd >> 4;                        // 16-byte chunks per lane: the pair of lanes alternates
 
-    for (int pg = pg_begin; pg < pg_end; ++pg) {
-        const int phys = trow[pg % p.ring_pages];
+    for (int it = it_begin; it < it_end; ++it) {
+        const int pg = it < n_front ? it : first_page + it - n_front;
+        const int phys = trow[pg < p.head_pages ? pg : p.head_pages + (pg - p.head_pages) % p.ring_pages];
         const size_t page_off = (size_t(phys) * p.nkv + g) * GB_PAGE * size_t(hd);
         const int kk = warp * AD_KEYS_PER_WARP + key_in_warp;
         const int j = pg * GB_PAGE + kk;
-        const bool valid = j >= lo && j <= pos;
+        const bool valid = j <= pos && (j >= lo || j < keep);
         // ---- scores of this warp's 16 keys; two lanes share a key and take its 16-byte chunks in turn
         float s[GT];
 #pragma unroll
@@ -156,7 +170,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
 #pragma unroll 4
         for (int k = 0; k < AD_KEYS_PER_WARP; ++k) {
             const int jk = first_key + k;
-            if (jk < lo || jk > pos) continue;          // uniform over the warp; unwritten rows are never read
+            if (jk > pos || (jk < lo && jk >= keep)) continue;          // uniform over the warp; unwritten rows are never read
             float2 vf[HC];
 #pragma unroll
             for (int c = 0; c < HC; ++c) {
@@ -200,7 +214,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
             o += acc_s[w][gi][d] * wgt;
         }
         if (p.splits == 1) {
-            p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(o / L);
+            p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(ad_gated(p, t, h0 + gi, d, o / L));
         } else {
             float* rec = p.scratch + ((size_t(t) * p.nh + h0 + gi) * p.splits + split) * (hd + 2);
             rec[d] = o;
@@ -228,7 +242,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
             L += __ldcg(rec + s * (hd + 2) + hd + 1) * wgt;
             o += __ldcg(rec + s * (hd + 2) + d) * wgt;
         }
-        p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(o / L);
+        p.out[size_t(t) * p.ldo + size_t(h0 + gi) * hd + d] = __float2bfloat16_rn(ad_gated(p, t, h0 + gi, d, o / L));
     }
     if (threadIdx.x == 0) p.counters[t * gridDim.y + ytile] = 0;
 }
@@ -260,15 +274,15 @@ GB_API int gb_attention_decode_supported(int hd, int cache_dtype, int q_dtype) {
     return cache_dtype == GB_BF16 && q_dtype == GB_BF16 && hd >= 16 && hd <= 256 && hd % 16 == 0;
 }
 
-// One token per sequence: q [T, nh*hd] bf16 (rotated), cache bf16.  splits chosen by the caller; scratch and counters (T * nkv * group tiles ints, zeroed) are
-// needed when splits > 1.
-GB_API int gb_attention_decode(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
-                               const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
-                               const void* kcache, const void* vcache, int window, float scale, int splits,
-                               float* scratch, int* counters, int n_counters, cudaStream_t stream) {
+static int attention_decode_launch(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
+                                   const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
+                                   const void* kcache, const void* vcache, int window, float scale, int splits,
+                                   float* scratch, int* counters, int n_counters, int head_pages, int keep_first,
+                                   const void* gate, long long ldg, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_decode_supported(hd, GB_BF16, GB_BF16), "gb_attention_decode: head_dim %d must be a multiple of 16 up to 256", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_decode: %d heads are not a multiple of %d KV heads", nh, nkv);
-    GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && splits >= 1, "gb_attention_decode: bad cache geometry");
+    GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && splits >= 1 && head_pages >= 0, "gb_attention_decode: bad cache geometry");
+    GB_REQUIRE(keep_first >= 0, "gb_attention_decode: a negative number of kept positions");
     GB_REQUIRE((ldq % 2) == 0 && (ldo % 2) == 0 && (reinterpret_cast<uintptr_t>(kcache) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(vcache) & 15) == 0, "gb_attention_decode: misaligned operands");
     if (T == 0) return 0;
@@ -281,6 +295,7 @@ GB_API int gb_attention_decode(const void* q, long long ldq, void* out, long lon
     p.vc = (const __nv_bfloat16*)vcache; p.seq_of = seq_of; p.pos = pos; p.table = table; p.scratch = scratch;
     p.counters = counters; p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.hd = hd; p.table_width = table_width;
     p.ring_pages = ring_pages; p.window = window; p.splits = splits; p.scale_log2 = scale * 1.4426950408889634f;
+    p.head_pages = head_pages; p.keep_first = keep_first; p.gate = (const __nv_bfloat16*)gate; p.ldg = ldg;
     dim3 grid(T, nkv * gtiles, splits);
     int hc = (hd + 63) / 64;
     switch (gt) {
@@ -289,4 +304,25 @@ GB_API int gb_attention_decode(const void* q, long long ldq, void* out, long lon
         case 4: return launch_ad_hc<4>(p, grid, hc, stream);
         default: return launch_ad_hc<8>(p, grid, hc, stream);
     }
+}
+
+// One token per sequence: q [T, nh*hd] bf16 (rotated), cache bf16.  splits chosen by the caller; scratch and counters (T * nkv * group tiles ints, zeroed) are
+// needed when splits > 1.
+GB_API int gb_attention_decode(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
+                               const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
+                               const void* kcache, const void* vcache, int window, float scale, int splits,
+                               float* scratch, int* counters, int n_counters, cudaStream_t stream) {
+    return attention_decode_launch(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, kcache, vcache,
+                                   window, scale, splits, scratch, counters, n_counters, 0, 0, nullptr, 0, stream);
+}
+
+// The same behind a window that keeps the sequence's first keep_first positions visible (their pages are the first
+// head_pages entries of the page table), the result multiplied by sigmoid(gate) when a gate [T, nh*hd] is given.
+GB_API int gb_attention_decode_kept(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
+                                    const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
+                                    const void* kcache, const void* vcache, int window, float scale, int splits,
+                                    float* scratch, int* counters, int n_counters, int head_pages, int keep_first,
+                                    const void* gate, long long ldg, cudaStream_t stream) {
+    return attention_decode_launch(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, kcache, vcache,
+                                   window, scale, splits, scratch, counters, n_counters, head_pages, keep_first, gate, ldg, stream);
 }

@@ -8,7 +8,9 @@
 // K and V pages are double-buffered in shared memory with cp.async.
 //
 // Sizes: head_dim 64 or 128 here (other sizes take the generic kernel), any group
-// size, any window, sequences that start anywhere in their cache.
+// size, any window, sequences that start anywhere in their cache.  Behind a window the
+// sequence's first keep_first positions may stay visible (their pages are walked first);
+// the result may be multiplied by sigmoid(gate) entry by entry.
 //
 // EXACT (for designs that ask for 32-bit attention weights): the weights p are not rounded to bfloat16.
 // Each p is split into three bfloat16 terms, p = hi + mid + lo (8 + 8 + 8 bits: all 24 of a float's
@@ -39,6 +41,10 @@ struct ApParams {
     long long ldq, ldo;
     int nh, nkv, table_width, ring_pages, window;
     float scale_log2;
+    int head_pages, keep_first;      // with a window: the sequence's first keep_first positions stay visible; their pages are
+                                     // the first head_pages entries of the table, in front of the ring
+    const __nv_bfloat16* gate;       // [T, nh*HD] or null: the result is multiplied by sigmoid(gate)
+    long long ldg;
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -108,9 +114,13 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
     const int pos_lo = start + q0, pos_hi = start + q0 + rows - 1;
     const int kb_begin = p.window > 0 ? max(0, pos_lo - p.window + 1) >> GB_PAGE_SHIFT : 0;
     const int kb_end = (pos_hi >> GB_PAGE_SHIFT) + 1;
+    // pages in front of the window that hold kept first positions come first in the walk
+    const int keep = p.window > 0 ? p.keep_first : 0;
+    const int n_front = min((keep + AP_BN - 1) >> GB_PAGE_SHIFT, kb_begin);
+    const int n_steps = n_front + kb_end - kb_begin;
 
     auto load_kv = [&](int kb, int buf) {
-        const int phys = trow[kb % p.ring_pages];
+        const int phys = trow[kb < p.head_pages ? kb : p.head_pages + (kb - p.head_pages) % p.ring_pages];
         const size_t off = (size_t(phys) * p.nkv + g) * AP_BN * size_t(HD);
         __nv_bfloat16* kd = ks + buf * AP_BN * HD;
         __nv_bfloat16* vd = vs + buf * AP_BN * HD;
@@ -127,7 +137,7 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
         int r = i / CH, c = i - r * CH;
         cp_async16(qs + swz<HD>(r, c), p.q + size_t(tok0 + min(r, rows - 1)) * p.ldq + size_t(h) * HD + c * 8, r < rows);
     }
-    load_kv(kb_begin, 0);
+    load_kv(n_front > 0 ? 0 : kb_begin, 0);
     cp_async_commit();
 
     // this thread's two query rows and their positions (-1: no such query)
@@ -140,9 +150,10 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
     for (int i = 0; i < OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    for (int kb = kb_begin; kb < kb_end; ++kb) {
-        const int buf = (kb - kb_begin) & 1;
-        if (kb + 1 < kb_end) load_kv(kb + 1, buf ^ 1);
+    for (int it = 0; it < n_steps; ++it) {
+        const int kb = it < n_front ? it : kb_begin + it - n_front;
+        const int buf = it & 1;
+        if (it + 1 < n_steps) load_kv(it + 1 < n_front ? it + 1 : kb_begin + it + 1 - n_front, buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -177,10 +188,10 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
         for (int j = 0; j < NT; ++j) {
             if (need_mask) {
                 int ka = key0 + 8 * j, kb2 = ka + 1;
-                if (ka > pq0 || ka < lo0) s[j][0] = -INFINITY;
-                if (kb2 > pq0 || kb2 < lo0) s[j][1] = -INFINITY;
-                if (ka > pq1 || ka < lo1) s[j][2] = -INFINITY;
-                if (kb2 > pq1 || kb2 < lo1) s[j][3] = -INFINITY;
+                if (ka > pq0 || (ka < lo0 && ka >= keep)) s[j][0] = -INFINITY;
+                if (kb2 > pq0 || (kb2 < lo0 && kb2 >= keep)) s[j][1] = -INFINITY;
+                if (ka > pq1 || (ka < lo1 && ka >= keep)) s[j][2] = -INFINITY;
+                if (kb2 > pq1 || (kb2 < lo1 && kb2 >= keep)) s[j][3] = -INFINITY;
             }
             mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
             mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
@@ -261,10 +272,25 @@ __global__ void __launch_bounds__(AP_THREADS, EXACT ? 1 : 2) attention_prefill_k
     const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
     __nv_bfloat16* out0 = p.out + size_t(tok0 + r0) * p.ldo + size_t(h) * HD + 2 * (lane & 3);
     __nv_bfloat16* out1 = p.out + size_t(tok0 + r1) * p.ldo + size_t(h) * HD + 2 * (lane & 3);
+    const __nv_bfloat16* g0 = p.gate ? p.gate + size_t(tok0 + r0) * p.ldg + size_t(h) * HD + 2 * (lane & 3) : nullptr;
+    const __nv_bfloat16* g1 = p.gate ? p.gate + size_t(tok0 + r1) * p.ldg + size_t(h) * HD + 2 * (lane & 3) : nullptr;
 #pragma unroll
     for (int i = 0; i < OT; ++i) {
-        if (r0 < rows) *reinterpret_cast<__nv_bfloat162*>(out0 + 8 * i) = __floats2bfloat162_rn(o[i][0] * inv0, o[i][1] * inv0);
-        if (r1 < rows) *reinterpret_cast<__nv_bfloat162*>(out1 + 8 * i) = __floats2bfloat162_rn(o[i][2] * inv1, o[i][3] * inv1);
+        float2 f0 = make_float2(inv0, inv0), f1 = make_float2(inv1, inv1);
+        if (p.gate) {
+            if (r0 < rows) {
+                const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g0 + 8 * i));
+                f0.x *= 1.f / (1.f + expf(-z.x));
+                f0.y *= 1.f / (1.f + expf(-z.y));
+            }
+            if (r1 < rows) {
+                const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g1 + 8 * i));
+                f1.x *= 1.f / (1.f + expf(-z.x));
+                f1.y *= 1.f / (1.f + expf(-z.y));
+            }
+        }
+        if (r0 < rows) *reinterpret_cast<__nv_bfloat162*>(out0 + 8 * i) = __floats2bfloat162_rn(o[i][0] * f0.x, o[i][1] * f0.y);
+        if (r1 < rows) *reinterpret_cast<__nv_bfloat162*>(out1 + 8 * i) = __floats2bfloat162_rn(o[i][2] * f1.x, o[i][3] * f1.y);
     }
 }
 
@@ -294,11 +320,14 @@ GB_API int gb_attention_prefill_tile() { return AP_BM; }
 GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long long ldo, int nh, int nkv, int hd,
                                 const int* tiles, int n_tiles, const int* cu, const int* starts, const int* qlens,
                                 const int* table, int table_width, int ring_pages, const void* kcache,
-                                const void* vcache, int window, float scale, int exact, cudaStream_t stream) {
+                                const void* vcache, int window, float scale, int exact, int head_pages, int keep_first,
+                                const void* gate, long long ldg, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_prefill_supported(hd, GB_BF16, GB_BF16), "gb_attention_prefill: head_dim %d is not 64 or 128", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_prefill: bad head counts %d / %d", nh, nkv);
     GB_REQUIRE(n_tiles <= 65535, "gb_attention_prefill: %d tiles of queries are too many for one launch", n_tiles);
-    GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0, "gb_attention_prefill: bad cache geometry");
+    GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && head_pages >= 0, "gb_attention_prefill: bad cache geometry");
+    GB_REQUIRE(keep_first >= 0, "gb_attention_prefill: a negative number of kept positions");
+    GB_REQUIRE(!gate || ((ldg % 2) == 0 && (reinterpret_cast<uintptr_t>(gate) & 3) == 0), "gb_attention_prefill: misaligned gate");
     GB_REQUIRE((ldq % 8) == 0 && (ldo % 2) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(kcache) & 15) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15) == 0,
                "gb_attention_prefill: misaligned operands");
@@ -308,6 +337,7 @@ GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long lo
     p.vc = (const __nv_bfloat16*)vcache; p.tiles = tiles; p.cu = cu; p.starts = starts; p.qlens = qlens; p.table = table;
     p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.table_width = table_width; p.ring_pages = ring_pages;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.head_pages = head_pages; p.keep_first = keep_first; p.gate = (const __nv_bfloat16*)gate; p.ldg = ldg;
     if (exact) return hd == 64 ? launch_ap<64, true>(p, n_tiles, stream) : launch_ap<128, true>(p, n_tiles, stream);
     return hd == 64 ? launch_ap<64, false>(p, n_tiles, stream) : launch_ap<128, false>(p, n_tiles, stream);
 }

@@ -297,6 +297,32 @@ def moe_down(y: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_down: 
     return out
 
 
+def moe_grouped_supported(h: torch.Tensor, w_gate: torch.Tensor) -> bool:
+    """Whether the tiled tensor-core kernels take these experts: bfloat16, K and F multiples of 8, aligned rows."""
+    return h.dtype == torch.bfloat16 and w_gate.dtype == torch.bfloat16 and h.stride(1) == 1 and h.stride(0) % 8 == 0 \
+        and h.data_ptr() % 16 == 0 and bool(native.library().gb_moe_grouped_supported(w_gate.shape[2], w_gate.shape[1]))
+
+
+def moe_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                w_down: torch.Tensor, limit: float, out: torch.Tensor, ctx, accumulate: bool = False) -> torch.Tensor:
+    """The routed experts of a step of many tokens on the tensor cores: the (token, choice) pairs sorted by expert on
+    the device, gate and up with the clamped unit, down, and the weighted sum per token; what moe_gate_up and moe_down
+    give, up to the rounding of bfloat16 unit outputs.  Four launches."""
+    _cuda(h, ids, weights, w_gate, w_up, w_down, out)
+    T, K = h.shape
+    E, F, _ = w_gate.shape
+    N, top = w_down.shape[1], ids.shape[1]
+    assert w_gate.shape == w_up.shape == (E, F, K) and w_down.shape == (E, N, F) and out.shape == (T, N) and out.dtype == torch.float32
+    assert w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and out.is_contiguous()
+    assert ids.shape == weights.shape == (T, top) and ids.is_contiguous() and weights.is_contiguous()
+    y = ctx.ws.get("moe.units", (T, top, F), torch.bfloat16)
+    z = ctx.ws.get("moe.rows", (T * top, N), torch.float32)
+    scratch = ctx.ws.get("moe.sorted", (native.library().gb_moe_grouped_scratch_ints(T, top, E),), torch.int32)
+    call("gb_moe_grouped", ptr(h), h.stride(0), T, K, F, N, E, top, ptr(ids), ptr(weights), ptr(w_gate), ptr(w_up), ptr(w_down),
+         float(limit), ptr(y), ptr(z), ptr(scratch), ptr(out), int(bool(accumulate)), stream_ptr())
+    return out
+
+
 UNARY_ACTS = {"silu": 1, "gelu_tanh": 2, "gelu": 3}
 
 
@@ -609,14 +635,19 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
                      seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
                      splits: Optional[int] = None, mma: Optional[bool] = None, max_kv: Optional[int] = None,
-                     rope: Optional[tuple] = None) -> torch.Tensor:
+                     rope: Optional[tuple] = None, keep_first: int = 0, head_pages: int = 0,
+                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per sequence over the bf16 cache; all heads of a group share one pass over
     the keys and values.  mma: the tensor-core kernel (head sizes 64 and 128; the default
     where it fits) or the CUDA-core one (any head size that is a multiple of 16).
     rope = (k, v, inv_freq, rotary_dim, pairing), tensor-core kernel only: q, k and v are the
     unrotated projections; the kernel rotates q and k and writes k and v into the cache itself
-    (k and v None: it reads another run's cache and only rotates q)."""
-    _cuda(q, out, seq_of, pos, table, kcache, vcache)
+    (k and v None: it reads another run's cache and only rotates q).
+    keep_first, head_pages, gate (CUDA-core kernel only): as attention_generic."""
+    _cuda(q, out, seq_of, pos, table, kcache, vcache, gate)
+    kept = bool(keep_first or head_pages or gate is not None)
+    assert not kept or (mma is False and rope is None)
+    assert gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape == out.shape)
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
@@ -641,6 +672,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
              n_kv_heads, head_dim, rotary_dim, pairing, ptr(inv_freq), ptr(seq_of), ptr(pos), ptr(table), table.shape[1],
              ring_pages, ptr(kcache), ptr(vcache), int(window or 0), float(scale), splits, ptr(scratch), ptr(counters),
              0 if counters is None else counters.numel(), stream_ptr())
+        return out
+    if kept:
+        call("gb_attention_decode_kept", ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
+             ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
+             float(scale), splits, ptr(scratch), ptr(counters), 0 if counters is None else counters.numel(), int(head_pages),
+             int(keep_first or 0), ptr(gate), 0 if gate is None else gate.stride(0), stream_ptr())
         return out
     call(entry, ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
          ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
@@ -673,17 +710,21 @@ def attention_prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor, head_d
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       tiles: torch.Tensor, cu: torch.Tensor, starts: torch.Tensor, qlens: torch.Tensor,
                       table: torch.Tensor, ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int,
-                      scale: float, tc: Optional[bool] = None, exact: bool = False) -> torch.Tensor:
+                      scale: float, tc: Optional[bool] = None, exact: bool = False, keep_first: int = 0, head_pages: int = 0,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Many tokens per sequence over the bf16 cache (which already holds their keys and
     values), flash style.  tc: both products on tcgen05 with S and PV in TMEM (the default where it
     fits), else on mma.sync; both take head sizes 64 and 128.  exact (mma.sync kernel only): the
-    attention weights stay 32-bit, split into three bfloat16 terms for the product with the values."""
-    _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache)
+    attention weights stay 32-bit, split into three bfloat16 terms for the product with the values.
+    keep_first, head_pages, gate (mma.sync kernel only): as attention_generic."""
+    _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache, gate)
+    assert gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape == out.shape)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (q.shape[0], n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    plain = not (exact or keep_first or head_pages or gate is not None)
     if tc is None:
-        tc = attention_prefill_tc_supported(q, kcache, head_dim) and not exact
-    assert not (tc and exact)
+        tc = attention_prefill_tc_supported(q, kcache, head_dim) and plain
+    assert not tc or plain
     if tc:
         assert kcache.is_contiguous() and vcache.is_contiguous()
         call("gb_attention_prefill_tc", ptr(q), q.stride(0), ptr(out), out.stride(0), q.shape[0], n_heads, n_kv_heads,
@@ -692,7 +733,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
         return out
     call("gb_attention_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), n_heads, n_kv_heads, head_dim, ptr(tiles),
          tiles.numel() // 2, ptr(cu), ptr(starts), ptr(qlens), ptr(table), table.shape[1], ring_pages, ptr(kcache),
-         ptr(vcache), int(window or 0), float(scale), int(bool(exact)), stream_ptr())
+         ptr(vcache), int(window or 0), float(scale), int(bool(exact)), int(head_pages), int(keep_first or 0), ptr(gate),
+         0 if gate is None else gate.stride(0), stream_ptr())
     return out
 
 

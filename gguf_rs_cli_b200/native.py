@@ -156,6 +156,9 @@ _SIGNATURES = {
     "gb_moe_gate_up": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _I, _P],
     "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P],
     "gb_unary_act": [_P, _I, _L, _I, _P],
+    "gb_moe_grouped_supported": [_I, _I],
+    "gb_moe_grouped_scratch_ints": [_I, _I, _I],
+    "gb_moe_grouped": [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "gb_glu_clamped": [_P, _L, _P, _I, _I, _I, _F, _P],
     "gb_qk_norm_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P],
     "gb_latent_prep": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _L, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _P],
@@ -175,6 +178,7 @@ _SIGNATURES = {
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
     "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
     "gb_attention_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
+    "gb_attention_decode_kept": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _I, _I, _P, _L, _P],
     "gb_attention_decode_mma": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
     "gb_attention_decode_mma_rope": [_P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I,
                                      _P, _P, _I, _P],
@@ -185,7 +189,7 @@ _SIGNATURES = {
     "gb_gemm_tc_set_stamps": [_P, _I, _I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
-    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P],
+    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _I, _I, _P, _L, _P],
     "gb_attention_prefill_supported": [_I, _I, _I],
     "gb_attention_prefill_tile": [],
     "gb_attention_prefill_tc": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _L, _I, _F, _P],
@@ -196,7 +200,7 @@ _SIGNATURES = {
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }
-_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
+_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_moe_grouped_scratch_ints": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:
@@ -232,7 +236,7 @@ def library():
 
 _launches = 0
 # kernels launched by one call of an entry point, where that is not one
-KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2, "gb_gla": 2}
+KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2, "gb_gla": 2, "gb_moe_grouped": 4}
 
 
 def launch_count() -> int:

@@ -158,7 +158,7 @@ class Attention(Part):
 
     def plan(self, batch: HostBatch):
         """Prompts: the list of query tiles (sequence row, first query) that the prefill kernel's CTAs take."""
-        if batch.decode or self.prepared or (self.exact and not self._exact_tiled()):
+        if batch.decode or (self.exact and not self._exact_tiled()):
             return {}
         return {"tiles": kernels.attention_prefill_tiles(batch.qlens)}
 
@@ -175,12 +175,10 @@ class Attention(Part):
     def graph_class(self, batch: HostBatch):
         """The decode kernel splits each sequence's pages over CTAs by a rule of the longest sequence; steps
         of one class launch the same grid and may share a captured graph."""
-        if self.prepared:
-            return ()                     # the general kernel: one block per token and head, whatever the lengths
         if self.exact:
             # the general kernel: one block per token and head, whatever the lengths; the CUDA-core decode kernel
             # splits each sequence's pages by a rule of the longest sequence
-            max_kv = min(batch.max_kv, self.window) if self.window else batch.max_kv
+            max_kv = min(batch.max_kv, self.window + self.keep_first) if self.window else batch.max_kv
             return ("cuda", kernels.decode_split_class_exact(max_kv)) if self._exact_decode() else ()
         return kernels.decode_split_class(min(batch.max_kv, self.window) if self.window else batch.max_kv)
 
@@ -219,9 +217,21 @@ class Attention(Part):
                                    run.ring_pages, run.head_pages, run.k, run.v)
         ctx.mark("heads")
         out = ctx.ws.get("attn.out", (T, nh * vd), ctx.dtype)
-        kernels.attention_generic(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
-                                  self.window or 0, self.scale, v_dim=vd, keep_first=self.keep_first,
-                                  head_pages=run.head_pages, gate=gate)
+        tiles = ctx.plan_of(self).get("tiles")
+        kept = dict(keep_first=self.keep_first, head_pages=run.head_pages, gate=gate)
+        if not ctx.decode and tiles is not None and self._exact_tiled() and kernels.attention_prefill_supported(q, run.k, hd):
+            # prompts, keys and values of 64 or 128 entries: the tiled kernel with 32-bit weights
+            kernels.attention_prefill(q, out, nh, nkv, hd, tiles, ctx.cu, ctx.starts, ctx.qlens, table, run.ring_pages,
+                                      run.k, run.v, self.window or 0, self.scale, tc=False, exact=True, **kept)
+        elif ctx.decode and self._exact_decode() and kernels.attention_decode_supported(q, run.k, hd):
+            # single tokens: one pass over a token's keys serves the heads of a group, 32-bit weights
+            max_kv = min(ctx.max_kv, self.window + self.keep_first) if self.window else ctx.max_kv
+            splits = kernels.decode_splits_exact(T, nh, nkv, max_kv, kernels.tc_scratch(q.device).sms)
+            kernels.attention_decode(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
+                                     self.window or 0, self.scale, mma=False, max_kv=max_kv, splits=splits, **kept)
+        else:
+            kernels.attention_generic(q, out, nh, nkv, hd, ctx.seq_of, ctx.pos, table, run.ring_pages, run.k, run.v,
+                                      self.window or 0, self.scale, v_dim=vd, **kept)
         ctx.mark("attention")
         term = self.o(out, ctx, out_dtype=torch.float32)
         ctx.mark("o")

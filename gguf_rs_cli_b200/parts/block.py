@@ -84,7 +84,11 @@ class OutputNormBlock:
         ctx.mark("mixer_norm")
         if self.feed_forward is None:
             return
-        term = self.feed_forward.forward(self._rows(stream, ctx), ctx)
+        if getattr(self.feed_forward, "reads_stream", False):
+            # a part that decides in 32-bit (a router) also gets the stream itself, not only its bfloat16 copy
+            term = self.feed_forward.forward(self._rows(stream, ctx), ctx, x32=stream.x)
+        else:
+            term = self.feed_forward.forward(self._rows(stream, ctx), ctx)
         self.norms["feed_forward"].add_normed(stream, term, ctx)
         ctx.mark("ff_norm")
 

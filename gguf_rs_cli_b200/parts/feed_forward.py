@@ -153,12 +153,15 @@ class RoutedExperts(Part):
             self.shared_gate_up = Linear(torch.cat([g, u.to(g.dtype)], dim=0), name="moe.shared_gate_up")
             self.shared_down = Linear(d, name="moe.shared_down")
 
+    TOKEN_BY_TOKEN = 16           # steps of at most this many tokens run every (token, choice) pair for itself
     graph_class = ()              # grids depend on the number of tokens only
+    reads_stream = True           # a block that has the rows in 32-bit gives them too (x32): the router reads those
 
-    def forward(self, h, ctx: StepContext) -> torch.Tensor:
+    def forward(self, h, ctx: StepContext, x32: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, E, top = h.shape[0], self.p["hidden_size"], self.top
-        # the router's logits in 32-bit sums (the rows may be the bfloat16 copy of the stream)
-        logits = kernels.gemm_generic(h, self.router.weight, None, ctx.ws.get("moe.logits", (T, self.n), torch.float32))
+        # the router's logits in 32-bit sums, from 32-bit rows where the block has them
+        logits = kernels.gemm_generic(h if x32 is None else x32, self.router.weight, None,
+                                      ctx.ws.get("moe.logits", (T, self.n), torch.float32))
         ids = ctx.ws.get("moe.ids", (T, top), torch.int32)
         weights = ctx.ws.get("moe.weights", (T, top), torch.float32)
         kernels.moe_route(logits, self.groups, self.keep, top, float(self.p.get("scale", 1.0)), ids, weights)
@@ -170,8 +173,13 @@ class RoutedExperts(Part):
                                       float(self.p["shared_limit"]))
             self.shared_down(act, ctx, out_dtype=torch.float32, buffer="moe.out")
             ctx.mark("shared")
-        y = ctx.ws.get("moe.units", (T, top, self.F), ctx.dtype)
-        kernels.moe_gate_up(h, ids, self.w_gate, self.w_up, float(self.p["limit"]), y)
-        kernels.moe_down(y, ids, weights, self.w_down, out, accumulate=bool(self.shared_ff))
+        if T > self.TOKEN_BY_TOKEN and kernels.moe_grouped_supported(h, self.w_gate):
+            # many tokens: pairs sorted by expert on the device, tiles of 64 pairs on the tensor cores
+            kernels.moe_grouped(h, ids, weights, self.w_gate, self.w_up, self.w_down, float(self.p["limit"]), out, ctx,
+                                accumulate=bool(self.shared_ff))
+        else:
+            y = ctx.ws.get("moe.units", (T, top, self.F), ctx.dtype)
+            kernels.moe_gate_up(h, ids, self.w_gate, self.w_up, float(self.p["limit"]), y)
+            kernels.moe_down(y, ids, weights, self.w_down, out, accumulate=bool(self.shared_ff))
         ctx.mark("experts")
         return out

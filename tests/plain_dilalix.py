@@ -132,16 +132,20 @@ def route(scores, top, n_groups, keep):
     return sorted(allowed, key=lambda e: (-float(scores[e]), e))[:top]
 
 
-def moe_ff(h, w, p, mlp):
+def moe_ff(h, w, p, mlp, chosen=None, scores_out=None):
+    """chosen: per token the experts to use in place of the router's choice (a caller that follows another
+    implementation through a near tie); scores_out: a list that receives the scores [n, experts]."""
     r = mlp["router"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     scores = torch.sigmoid(lin(h, w[p + "router"]))
+    if scores_out is not None:
+        scores_out.append(scores)
     for t in range(h.shape[0]):
-        chosen = route(scores[t], r["top"], groups["count"], groups["keep"])
-        s = scores[t][chosen]
+        picked = route(scores[t], r["top"], groups["count"], groups["keep"]) if chosen is None else list(chosen[t])
+        s = scores[t][picked]
         weights = s / (s.sum() + 1e-20) * r["scale"]
-        for e, a in zip(chosen, weights):
+        for e, a in zip(picked, weights):
             out[t] += a * expert(h[t:t + 1], w, f"{p}e{e}.", mlp["expert"]["limit"])[0]
     if mlp.get("shared"):
         out = out + expert(h, w, p + "shared.", mlp["shared"]["limit"])
@@ -149,8 +153,9 @@ def moe_ff(h, w, p, mlp):
 
 
 # ------------------------------------------------------------------- the model
-def forward(cfg, w, tokens, dtype=torch.float64, layers_out=None):
-    """Logits [n, vocab] of one sequence.  layers_out: a list that receives the residual stream after each layer."""
+def forward(cfg, w, tokens, dtype=torch.float64, layers_out=None, routes=None, scores_out=None):
+    """Logits [n, vocab] of one sequence.  layers_out: a list that receives the residual stream after each layer.
+    routes {layer: experts per token} replaces the routers' choices; scores_out {layer: scores} receives theirs."""
     eps = cfg["norm"]["eps"]
     w = {k: v.to(dtype) for k, v in w.items()}
     x = w["embed"][torch.tensor(tokens)]
@@ -168,7 +173,13 @@ def forward(cfg, w, tokens, dtype=torch.float64, layers_out=None):
         x = x + rms(y, w[f"l{i}.norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = dense_ff(x, w, f"l{i}.mlp.") if mlp["kind"] == "dense" else moe_ff(x, w, f"l{i}.mlp.", mlp)
+            if mlp["kind"] == "dense":
+                y = dense_ff(x, w, f"l{i}.mlp.")
+            else:
+                got = []
+                y = moe_ff(x, w, f"l{i}.mlp.", mlp, None if routes is None else routes.get(i), got)
+                if scores_out is not None:
+                    scores_out[i] = got[0]
             x = x + rms(y, w[f"l{i}.norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
