@@ -342,7 +342,10 @@ def stage_times(llm, lens, starts=0, reps=3):
         slots = [eng.open() for _ in lens]
         if starts:
             eng.step([Entry(s, [1] * starts, ()) for s in slots])
-        ctx, _, _ = eng.plan([Entry(s, [1] * n, ()) for s, n in zip(slots, lens)])
+        # random token ids: a router sends equal tokens to equal experts, which would flatter its kernels
+        g = torch.Generator().manual_seed(11 + rep)
+        ids = [torch.randint(0, model.spec.vocab_size, (n,), generator=g).tolist() for n in lens]
+        ctx, _, _ = eng.plan([Entry(s, t, ()) for s, t in zip(slots, ids)])
         ctx.marks, ctx.mark_detail = [], True
         stream = Stream(model.embedding.forward(ctx.tokens, ctx))
         kinds = []

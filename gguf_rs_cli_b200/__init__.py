@@ -1,4 +1,4 @@
-"""A small, whole library for the Llama dense decoder (and the Debonex hybrid decoder) on one
+"""A small, whole library for the Llama dense decoder (and the Debonex and Dilalix hybrid decoders) on one
 NVIDIA B200: from a model folder (config.json + safetensors) or random weights to generated token
 ids, on hand-written sm_100a kernels.  config/, weights/, parts/, cache/, engine/ and sampling/ hold the
 library, csrc/ the kernels, api.py and cli.py the two ways in."""

@@ -32,7 +32,7 @@ def parse_stop_ids(text: str) -> List[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="gguf_rs_cli_b200", description="Generation on one B200 (Llama, Debonex): token ids in, token ids out")
+    ap = argparse.ArgumentParser(prog="gguf_rs_cli_b200", description="Generation on one B200 (Llama, Debonex, Dilalix): token ids in, token ids out")
     src = ap.add_mutually_exclusive_group(required=True)
     src.add_argument("-m", "--model", help="folder with config.json and model.safetensors")
     src.add_argument("--random", metavar="CONFIG_JSON", help="random weights N(0, 0.02) for this config.json")

@@ -13,16 +13,20 @@
 constexpr int MOE_MAX_EXPERTS = 1024;
 constexpr int MOE_MAX_TOP = 32;
 
-__global__ void __launch_bounds__(32) moe_route_kernel(const float* __restrict__ z, int E, int n_groups, int keep, int top,
-                                                       float scale, int* __restrict__ ids, float* __restrict__ weights) {
-    __shared__ float s[MOE_MAX_EXPERTS];
-    __shared__ float mark[MOE_MAX_EXPERTS];
-    __shared__ unsigned char open_[MOE_MAX_EXPERTS];        // 1: the expert may still be chosen
-    __shared__ int chosen[MOE_MAX_TOP];
-    const int t = blockIdx.x, lane = threadIdx.x;
+static int moe_smem(const void* kernel, size_t bytes, const char* what) {
+    if (bytes <= 48 * 1024) return 0;
+    if (bytes > 200 * 1024) return gb_fail("%s: rows of %zu bytes do not fit shared memory", what, bytes);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess)
+        return gb_fail("%s: cannot get %zu bytes of shared memory", what, bytes);
+    return 0;
+}
+
+// The choice for one token by one warp; z: the token's logits (shared or global memory).
+__device__ void moe_route_warp(const float* z, int E, int n_groups, int keep, int top, float scale, int* __restrict__ ids,
+                               float* __restrict__ weights, float* s, float* mark, unsigned char* open_, int* chosen, int lane) {
     const int size = E / n_groups;
     for (int e = lane; e < E; e += 32) {
-        s[e] = 1.f / (1.f + expf(-z[size_t(t) * E + e]));
+        s[e] = 1.f / (1.f + expf(-z[e]));
         open_[e] = 0;
     }
     __syncwarp();
@@ -71,9 +75,20 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const float* __restrict__
         __syncwarp();
     }
     for (int r = lane; r < top; r += 32) {
-        ids[size_t(t) * top + r] = chosen[r];
-        weights[size_t(t) * top + r] = s[chosen[r]] / (sum + 1e-20f) * scale;
+        ids[r] = chosen[r];
+        weights[r] = s[chosen[r]] / (sum + 1e-20f) * scale;
     }
+}
+
+__global__ void __launch_bounds__(32) moe_route_kernel(const float* __restrict__ z, int E, int n_groups, int keep, int top,
+                                                       float scale, int* __restrict__ ids, float* __restrict__ weights) {
+    __shared__ float s[MOE_MAX_EXPERTS];
+    __shared__ float mark[MOE_MAX_EXPERTS];
+    __shared__ unsigned char open_[MOE_MAX_EXPERTS];        // 1: the expert may still be chosen
+    __shared__ int chosen[MOE_MAX_TOP];
+    const int t = blockIdx.x;
+    moe_route_warp(z + size_t(t) * E, E, n_groups, keep, top, scale, ids + size_t(t) * top, weights + size_t(t) * top, s, mark,
+                   open_, chosen, threadIdx.x);
 }
 
 // z float32 [T, E] router logits -> ids int32 [T, top], weights float32 [T, top], largest score first.
@@ -88,10 +103,38 @@ GB_API int gb_moe_route(const float* z, int T, int E, int n_groups, int keep, in
     return 0;
 }
 
+// The router's product and the choice in one kernel: one block per token; the token's row lies in shared memory as
+// 32-bit floats, the warps take the experts' rows in turn (32-bit sums), the first warp then chooses.
+template <typename TW>
+__device__ __forceinline__ float moe_row_dot(const TW* __restrict__ w, const float* __restrict__ hs, int K, int lane);
+
+template <typename TW>
+__global__ void __launch_bounds__(128) moe_router_kernel(const void* __restrict__ x, int x_dtype, long long ldx, int K,
+                                                         const TW* __restrict__ w, int E, int n_groups, int keep, int top,
+                                                         float scale, int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float moe_xs[];
+    __shared__ float z[MOE_MAX_EXPERTS];
+    __shared__ float s[MOE_MAX_EXPERTS];
+    __shared__ float mark[MOE_MAX_EXPERTS];
+    __shared__ unsigned char open_[MOE_MAX_EXPERTS];
+    __shared__ int chosen[MOE_MAX_TOP];
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) moe_xs[i] = gb_load(x, x_dtype, size_t(t) * ldx + i);
+    __syncthreads();
+    for (int e = warp; e < E; e += 4) {
+        const float v = gb_warp_sum(moe_row_dot<TW>(w + size_t(e) * K, moe_xs, K, lane));
+        if (lane == 0) z[e] = v;
+    }
+    __syncthreads();
+    if (warp == 0)
+        moe_route_warp(z, E, n_groups, keep, top, scale, ids + size_t(t) * top, weights + size_t(t) * top, s, mark, open_, chosen, lane);
+}
+
 // ---------------------------------------------------------------- experts, token by token
 // y[t, r, f] = unit(Wg[e] h_t, Wu[e] h_t)_f with e = ids[t, r]; unit = gb_act_glu_clamped.  One block per (token,
 // choice) and slice of 32 features; the token's row lies in shared memory as 32-bit floats, a warp takes a feature at a
 // time and its lanes share the two matrix rows in pieces of eight (bfloat16) or four (float32) entries.
+// a lane's share of the product of a matrix row with the row in shared memory; the caller sums over the lanes
 template <typename TW>
 __device__ __forceinline__ float moe_row_dot(const TW* __restrict__ w, const float* __restrict__ hs, int K, int lane);
 
@@ -112,7 +155,7 @@ __device__ __forceinline__ float moe_row_dot<__nv_bfloat16>(const __nv_bfloat16*
     } else {
         for (int i = lane; i < K; i += 32) acc = fmaf(__bfloat162float(w[i]), hs[i], acc);
     }
-    return gb_warp_sum(acc);
+    return acc;
 }
 template <>
 __device__ __forceinline__ float moe_row_dot<float>(const float* __restrict__ w, const float* __restrict__ hs, int K, int lane) {
@@ -128,10 +171,10 @@ __device__ __forceinline__ float moe_row_dot<float>(const float* __restrict__ w,
     } else {
         for (int i = lane; i < K; i += 32) acc = fmaf(w[i], hs[i], acc);
     }
-    return gb_warp_sum(acc);
+    return acc;
 }
 
-constexpr int MOE_SLICE = 32;
+constexpr int MOE_SLICE = 16;
 
 template <typename TW>
 __global__ void __launch_bounds__(128) moe_gate_up_kernel(const void* __restrict__ h, int h_dtype, long long ldh, int K, int F,
@@ -147,8 +190,10 @@ __global__ void __launch_bounds__(128) moe_gate_up_kernel(const void* __restrict
     const int f_end = min(F, (blockIdx.y + 1) * MOE_SLICE);
     for (int f = blockIdx.y * MOE_SLICE + warp; f < f_end; f += 4) {
         const size_t row = (size_t(e) * F + f) * K;
-        const float g = moe_row_dot<TW>(wg + row, moe_hs, K, lane);
-        const float u = moe_row_dot<TW>(wu + row, moe_hs, K, lane);
+        float g = moe_row_dot<TW>(wg + row, moe_hs, K, lane);
+        float u = moe_row_dot<TW>(wu + row, moe_hs, K, lane);
+        g = gb_warp_sum(g);
+        u = gb_warp_sum(u);
         if (lane == 0) gb_store(y, y_dtype, size_t(pair) * F + f, gb_act_glu_clamped(g, u, limit));
     }
 }
@@ -167,20 +212,35 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const void* __restrict__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_end = min(N, (blockIdx.y + 1) * MOE_SLICE);
     for (int n = blockIdx.y * MOE_SLICE + warp; n < n_end; n += 4) {
-        float acc = 0.f;
+        float acc = 0.f;                                  // the choices in their order, lane by lane; one sum over the lanes
+#pragma unroll 4
         for (int r = 0; r < top; ++r) {
             const int e = ids[size_t(t) * top + r];
             acc += moe_row_dot<TW>(wd + (size_t(e) * N + n) * F, moe_ys + r * F, F, lane);
         }
+        acc = gb_warp_sum(acc);
         if (lane == 0) out[size_t(t) * N + n] = accumulate ? out[size_t(t) * N + n] + acc : acc;
     }
 }
 
-static int moe_smem(const void* kernel, size_t bytes, const char* what) {
-    if (bytes <= 48 * 1024) return 0;
-    if (bytes > 200 * 1024) return gb_fail("%s: rows of %zu bytes do not fit shared memory", what, bytes);
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess)
-        return gb_fail("%s: cannot get %zu bytes of shared memory", what, bytes);
+
+// x [T, K] rows ldx apart (the rows the router reads, 32-bit where the caller has them); w [E, K] contiguous.
+GB_API int gb_moe_router(const void* x, int x_dtype, long long ldx, int T, int K, const void* w, int w_dtype, int E, int n_groups,
+                         int keep, int top, float scale, int* ids, float* weights, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(x_dtype) && gb_is_dtype(w_dtype), "gb_moe_router: bad dtype");
+    GB_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS && K > 0, "gb_moe_router: %d experts (1..%d)", E, MOE_MAX_EXPERTS);
+    GB_REQUIRE(n_groups > 0 && E % n_groups == 0 && keep > 0 && keep <= n_groups, "gb_moe_router: %d experts in %d groups, %d kept", E, n_groups, keep);
+    GB_REQUIRE(top > 0 && top <= MOE_MAX_TOP && top <= keep * (E / n_groups), "gb_moe_router: %d experts cannot be chosen from %d groups of %d (at most %d)", top, keep, E / n_groups, MOE_MAX_TOP);
+    if (T == 0) return 0;
+    const size_t smem = size_t(K) * 4;
+    if (w_dtype == GB_F32) {
+        if (moe_smem((const void*)moe_router_kernel<float>, smem + 16 * 1024, "gb_moe_router")) return 1;
+        moe_router_kernel<float><<<T, 128, smem, stream>>>(x, x_dtype, ldx, K, (const float*)w, E, n_groups, keep, top, scale, ids, weights);
+    } else {
+        if (moe_smem((const void*)moe_router_kernel<__nv_bfloat16>, smem + 16 * 1024, "gb_moe_router")) return 1;
+        moe_router_kernel<__nv_bfloat16><<<T, 128, smem, stream>>>(x, x_dtype, ldx, K, (const __nv_bfloat16*)w, E, n_groups, keep, top, scale, ids, weights);
+    }
+    GB_LAUNCH_OK("gb_moe_router");
     return 0;
 }
 

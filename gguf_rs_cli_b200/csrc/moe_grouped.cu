@@ -13,7 +13,9 @@
 
 namespace {
 
-constexpr int MG_BM = 64;           // pairs per tile
+constexpr int MG_BM = 64;           // pairs per tile (128, two row fragments a warp: the same time, 0.82 + 0.48 ms at 8,192 pairs)
+constexpr int MG_WM = MG_BM / 64;   // fragments of 16 rows per warp (four warps share a tile's rows)
+constexpr int MG_STAGES = 3;
 constexpr int MG_BN = 64;           // features per tile
 constexpr int MG_BK = 64;           // entries of K per stage
 constexpr int MG_THREADS = 128;
@@ -86,12 +88,14 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_kernel(const MgParams 
     constexpr int STAGE = (MG_BM + NB * MG_BN) * MG_BK;                 // elements per stage
     __nv_bfloat16* sm = reinterpret_cast<__nv_bfloat16*>(mg_smem);
     __shared__ int rows[MG_BM];
-    if (int(blockIdx.x) >= p.n_tiles[0]) return;
-    const int e = p.tiles[2 * blockIdx.x], place0 = p.tiles[2 * blockIdx.x + 1];
+    // blockIdx.x (which varies fastest in the order CTAs start) is the slice of features, blockIdx.y the tile of pairs:
+    // CTAs that run together share a tile's gathered rows and walk through one expert's matrix
+    if (int(blockIdx.y) >= p.n_tiles[0]) return;
+    const int e = p.tiles[2 * blockIdx.y], place0 = p.tiles[2 * blockIdx.y + 1];
     const int n_rows = min(MG_BM, p.offsets[e + 1] - place0);
-    const int n0 = blockIdx.y * MG_BN;
+    const int n0 = blockIdx.x * MG_BN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < MG_BM) rows[tid] = tid < n_rows ? p.perm[place0 + tid] : -1;
+    for (int i = tid; i < MG_BM; i += MG_THREADS) rows[i] = i < n_rows ? p.perm[place0 + i] : -1;
     __syncthreads();
     const __nv_bfloat16* w0 = p.w0 + size_t(e) * p.N * p.K;
     const __nv_bfloat16* w1 = GLU ? p.w1 + size_t(e) * p.N * p.K : nullptr;
@@ -116,26 +120,32 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_kernel(const MgParams 
         }
     };
 
-    float acc[NB][MG_BN / 8][4];
+    float acc[NB][MG_WM][MG_BN / 8][4];
 #pragma unroll
     for (int m = 0; m < NB; ++m)
 #pragma unroll
-        for (int j = 0; j < MG_BN / 8; ++j) acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f;
+        for (int mi = 0; mi < MG_WM; ++mi)
+#pragma unroll
+            for (int j = 0; j < MG_BN / 8; ++j) acc[m][mi][j][0] = acc[m][mi][j][1] = acc[m][mi][j][2] = acc[m][mi][j][3] = 0.f;
 
     const int k_steps = (p.K + MG_BK - 1) / MG_BK;
     load(0, 0);
     asm volatile("cp.async.commit_group;" ::: "memory");
+    if (k_steps > 1) load(MG_BK, 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
     for (int ks = 0; ks < k_steps; ++ks) {
-        const int stage = ks & 1;
-        if (ks + 1 < k_steps) load((ks + 1) * MG_BK, stage ^ 1);
-        asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
-        __syncthreads();
-        const __nv_bfloat16* as = sm + stage * STAGE;
+        __syncthreads();                                     // stage ks has landed; everyone is done with stage ks - 1
+        if (ks + 2 < k_steps) load((ks + 2) * MG_BK, (ks + 2) % MG_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const __nv_bfloat16* as = sm + (ks % MG_STAGES) * STAGE;
 #pragma unroll
         for (int k = 0; k < MG_BK / 16; ++k) {
-            unsigned af[4];
-            mg_ldmatrix_x4(af[0], af[1], af[2], af[3], as + mg_swz(warp * 16 + (lane & 15), 2 * k + (lane >> 4)));
+            unsigned af[MG_WM][4];
+#pragma unroll
+            for (int mi = 0; mi < MG_WM; ++mi)
+                mg_ldmatrix_x4(af[mi][0], af[mi][1], af[mi][2], af[mi][3],
+                               as + mg_swz(warp * 16 * MG_WM + mi * 16 + (lane & 15), 2 * k + (lane >> 4)));
 #pragma unroll
             for (int m = 0; m < NB; ++m) {
                 const __nv_bfloat16* bs = as + (MG_BM + m * MG_BN) * MG_BK;
@@ -143,16 +153,20 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_kernel(const MgParams 
                 for (int j2 = 0; j2 < MG_BN / 16; ++j2) {
                     unsigned b0, b1, b2, b3;
                     mg_ldmatrix_x4(b0, b1, b2, b3, bs + mg_swz(j2 * 16 + (lane & 7) + ((lane >> 4) << 3), 2 * k + ((lane >> 3) & 1)));
-                    mg_mma(acc[m][2 * j2], af, b0, b1);
-                    mg_mma(acc[m][2 * j2 + 1], af, b2, b3);
+#pragma unroll
+                    for (int mi = 0; mi < MG_WM; ++mi) {
+                        mg_mma(acc[m][mi][2 * j2], af[mi], b0, b1);
+                        mg_mma(acc[m][mi][2 * j2 + 1], af[mi], b2, b3);
+                    }
                 }
             }
         }
-        __syncthreads();
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+#pragma unroll
+    for (int mi = 0; mi < MG_WM; ++mi) {
+    const int r0 = warp * 16 * MG_WM + mi * 16 + (lane >> 2), r1 = r0 + 8;
     const int pair0 = rows[r0], pair1 = rows[r1];
 #pragma unroll
     for (int j = 0; j < MG_BN / 8; ++j) {
@@ -162,24 +176,25 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_kernel(const MgParams 
         if (GLU) {
             __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.out);
             if (pair0 >= 0) {
-                y[size_t(pair0) * p.N + n] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][j][0], acc[NB - 1][j][0], p.limit));
-                if (two) y[size_t(pair0) * p.N + n + 1] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][j][1], acc[NB - 1][j][1], p.limit));
+                y[size_t(pair0) * p.N + n] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][mi][j][0], acc[NB - 1][mi][j][0], p.limit));
+                if (two) y[size_t(pair0) * p.N + n + 1] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][mi][j][1], acc[NB - 1][mi][j][1], p.limit));
             }
             if (pair1 >= 0) {
-                y[size_t(pair1) * p.N + n] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][j][2], acc[NB - 1][j][2], p.limit));
-                if (two) y[size_t(pair1) * p.N + n + 1] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][j][3], acc[NB - 1][j][3], p.limit));
+                y[size_t(pair1) * p.N + n] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][mi][j][2], acc[NB - 1][mi][j][2], p.limit));
+                if (two) y[size_t(pair1) * p.N + n + 1] = __float2bfloat16_rn(gb_act_glu_clamped(acc[0][mi][j][3], acc[NB - 1][mi][j][3], p.limit));
             }
         } else {
             float* z = reinterpret_cast<float*>(p.out);
             if (pair0 >= 0) {
-                z[size_t(pair0) * p.N + n] = acc[0][j][0];
-                if (two) z[size_t(pair0) * p.N + n + 1] = acc[0][j][1];
+                z[size_t(pair0) * p.N + n] = acc[0][mi][j][0];
+                if (two) z[size_t(pair0) * p.N + n + 1] = acc[0][mi][j][1];
             }
             if (pair1 >= 0) {
-                z[size_t(pair1) * p.N + n] = acc[0][j][2];
-                if (two) z[size_t(pair1) * p.N + n + 1] = acc[0][j][3];
+                z[size_t(pair1) * p.N + n] = acc[0][mi][j][2];
+                if (two) z[size_t(pair1) * p.N + n + 1] = acc[0][mi][j][3];
             }
         }
+    }
     }
 }
 
@@ -221,22 +236,23 @@ GB_API int gb_moe_grouped(const void* h, long long ldh, int T, int K, int F, int
     moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, pairs, E, offsets, perm, tiles, n_tiles);
     GB_LAUNCH_OK("gb_moe_grouped (sort)");
     static bool configured = false;
-    constexpr int SMEM_GLU = 2 * (MG_BM + 2 * MG_BN) * MG_BK * 2, SMEM_ONE = 2 * (MG_BM + MG_BN) * MG_BK * 2;
+    constexpr int SMEM_GLU = MG_STAGES * (MG_BM + 2 * MG_BN) * MG_BK * 2, SMEM_ONE = MG_STAGES * (MG_BM + MG_BN) * MG_BK * 2;
     if (!configured) {
-        if (cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GLU) != cudaSuccess)
+        if (cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GLU) != cudaSuccess ||
+            cudaFuncSetAttribute(moe_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ONE) != cudaSuccess)
             return gb_fail("gb_moe_grouped: cannot get %d bytes of shared memory", SMEM_GLU);
         configured = true;
     }
-    GB_REQUIRE((F + MG_BN - 1) / MG_BN <= 65535 && (N + MG_BN - 1) / MG_BN <= 65535, "gb_moe_grouped: matrices too wide");
+    GB_REQUIRE(max_tiles <= 65535, "gb_moe_grouped: %d tiles of pairs are too many for one launch", max_tiles);
     MgParams p;
     p.a = (const __nv_bfloat16*)h; p.w0 = (const __nv_bfloat16*)wg; p.w1 = (const __nv_bfloat16*)wu; p.out = y;
     p.offsets = offsets; p.perm = perm; p.tiles = tiles; p.n_tiles = n_tiles; p.lda = ldh; p.a_div = top; p.N = F; p.K = K;
     p.limit = limit;
-    moe_grouped_kernel<true><<<dim3(max_tiles, (F + MG_BN - 1) / MG_BN), MG_THREADS, SMEM_GLU, stream>>>(p);
+    moe_grouped_kernel<true><<<dim3((F + MG_BN - 1) / MG_BN, max_tiles), MG_THREADS, SMEM_GLU, stream>>>(p);
     GB_LAUNCH_OK("gb_moe_grouped (gate, up)");
     p.a = (const __nv_bfloat16*)y; p.w0 = (const __nv_bfloat16*)wd; p.w1 = nullptr; p.out = z; p.lda = F; p.a_div = 1;
     p.N = N; p.K = F;
-    moe_grouped_kernel<false><<<dim3(max_tiles, (N + MG_BN - 1) / MG_BN), MG_THREADS, SMEM_ONE, stream>>>(p);
+    moe_grouped_kernel<false><<<dim3((N + MG_BN - 1) / MG_BN, max_tiles), MG_THREADS, SMEM_ONE, stream>>>(p);
     GB_LAUNCH_OK("gb_moe_grouped (down)");
     const long long total = (long long)T * N;
     moe_combine_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(z, weights, top, N, out, accumulate, total);

@@ -269,6 +269,17 @@ def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, scale: f
     call("gb_moe_route", ptr(logits), T, E, int(n_groups), int(keep), int(top), float(scale), ptr(ids), ptr(weights), stream_ptr())
 
 
+def moe_router(x: torch.Tensor, w: torch.Tensor, n_groups: int, keep: int, top: int, scale: float, ids: torch.Tensor,
+               weights: torch.Tensor) -> None:
+    """The router's product x w^T (32-bit sums) and the choice of moe_route in one kernel; x [T, K], w [experts, K]."""
+    _cuda(x, w, ids, weights)
+    T, K = x.shape
+    assert x.stride(1) == 1 and w.is_contiguous() and w.shape[1] == K and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    assert ids.shape == (T, top) and weights.shape == (T, top) and ids.is_contiguous() and weights.is_contiguous()
+    call("gb_moe_router", ptr(x), dtype_code(x), x.stride(0), T, K, ptr(w), dtype_code(w), w.shape[0], int(n_groups), int(keep),
+         int(top), float(scale), ptr(ids), ptr(weights), stream_ptr())
+
+
 def moe_gate_up(h: torch.Tensor, ids: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, limit: float,
                 y: torch.Tensor) -> torch.Tensor:
     """y[t, r, :] = unit(W_gate[e] h_t, W_up[e] h_t), e = ids[t, r]; unit(g, u) = g' sigmoid(1.702 g') (u' + 1) with

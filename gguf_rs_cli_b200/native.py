@@ -152,6 +152,7 @@ _SIGNATURES = {
                               _I, _I, _I, _P, _P, _I, _P],
     "gb_gla": [_P, _P, _P, _I, _L, _P, _I, _L, _P, _I, _F, _F, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "gb_gla_scratch_floats": [_I, _I, _I, _I],
+    "gb_moe_router": [_P, _I, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "gb_moe_route": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "gb_moe_gate_up": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _I, _P],
     "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P],

@@ -159,12 +159,11 @@ class RoutedExperts(Part):
 
     def forward(self, h, ctx: StepContext, x32: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, E, top = h.shape[0], self.p["hidden_size"], self.top
-        # the router's logits in 32-bit sums, from 32-bit rows where the block has them
-        logits = kernels.gemm_generic(h if x32 is None else x32, self.router.weight, None,
-                                      ctx.ws.get("moe.logits", (T, self.n), torch.float32))
+        # the router's product in 32-bit sums, from 32-bit rows where the block has them, and its choice
         ids = ctx.ws.get("moe.ids", (T, top), torch.int32)
         weights = ctx.ws.get("moe.weights", (T, top), torch.float32)
-        kernels.moe_route(logits, self.groups, self.keep, top, float(self.p.get("scale", 1.0)), ids, weights)
+        kernels.moe_router(h if x32 is None else x32, self.router.weight, self.groups, self.keep, top,
+                           float(self.p.get("scale", 1.0)), ids, weights)
         ctx.mark("router")
         out = ctx.ws.get("moe.out", (T, E), torch.float32)
         if self.shared_ff:
