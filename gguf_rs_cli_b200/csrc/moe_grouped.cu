@@ -17,7 +17,8 @@ constexpr int MG_BM = 64;           // pairs per tile (128, two row fragments a 
 constexpr int MG_WM = MG_BM / 64;   // fragments of 16 rows per warp (four warps share a tile's rows)
 constexpr int MG_STAGES = 3;
 constexpr int MG_BN = 64;           // features per tile
-constexpr int MG_BK = 64;           // entries of K per stage
+constexpr int MG_BK = 32;           // entries of K per stage: 12 KB a stage with gate and up, so that five CTAs share an SM
+constexpr int MG_CH = MG_BK / 8;    // 16-byte chunks per row of a stage
 constexpr int MG_THREADS = 128;
 
 __device__ __forceinline__ void mg_cp16(void* dst, const void* src, bool valid) {
@@ -34,8 +35,9 @@ __device__ __forceinline__ void mg_mma(float* c, const unsigned* a, unsigned b0,
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// element offset of (row, 16-byte chunk) in a tile of rows of 64 bfloat16, chunks XOR-swizzled by the row
-__device__ __forceinline__ int mg_swz(int row, int chunk) { return row * MG_BK + (((chunk ^ row) & 7) << 3); }
+// element offset of (row, 16-byte chunk) in a tile of rows of 32 bfloat16 (four chunks); two rows fill the 128 bytes that
+// the banks span, so the chunk is XOR-swizzled by the row pair: eight consecutive rows of one chunk fall into eight bank groups
+__device__ __forceinline__ int mg_swz(int row, int chunk) { return row * MG_BK + ((chunk ^ ((row >> 1) & 3)) << 3); }
 
 }  // namespace
 
@@ -82,7 +84,7 @@ struct MgParams {
 };
 
 template <bool GLU>
-__global__ void __launch_bounds__(MG_THREADS) moe_grouped_kernel(const MgParams p) {
+__global__ void __launch_bounds__(MG_THREADS, 5) moe_grouped_kernel(const MgParams p) {
     extern __shared__ __align__(128) unsigned char mg_smem[];
     constexpr int NB = GLU ? 2 : 1;
     constexpr int STAGE = (MG_BM + NB * MG_BN) * MG_BK;                 // elements per stage
@@ -102,8 +104,8 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_kernel(const MgParams 
 
     auto load = [&](int k0, int stage) {
         __nv_bfloat16* as = sm + stage * STAGE;
-        for (int i = tid; i < MG_BM * 8; i += MG_THREADS) {
-            const int r = i >> 3, c = i & 7;
+        for (int i = tid; i < MG_BM * MG_CH; i += MG_THREADS) {
+            const int r = i / MG_CH, c = i % MG_CH;
             const int pair = rows[r];
             const bool ok = pair >= 0 && k0 + c * 8 < p.K;
             mg_cp16(as + mg_swz(r, c), p.a + size_t(ok ? pair / p.a_div : 0) * p.lda + (ok ? k0 + c * 8 : 0), ok);
@@ -112,8 +114,8 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_kernel(const MgParams 
         for (int m = 0; m < NB; ++m) {
             __nv_bfloat16* bs = as + (MG_BM + m * MG_BN) * MG_BK;
             const __nv_bfloat16* w = m ? w1 : w0;
-            for (int i = tid; i < MG_BN * 8; i += MG_THREADS) {
-                const int r = i >> 3, c = i & 7;
+            for (int i = tid; i < MG_BN * MG_CH; i += MG_THREADS) {
+                const int r = i / MG_CH, c = i % MG_CH;
                 const bool ok = n0 + r < p.N && k0 + c * 8 < p.K;
                 mg_cp16(bs + mg_swz(r, c), w + (ok ? size_t(n0 + r) * p.K + k0 + c * 8 : 0), ok);
             }

@@ -296,15 +296,17 @@ def moe_gate_up(h: torch.Tensor, ids: torch.Tensor, w_gate: torch.Tensor, w_up: 
 
 
 def moe_down(y: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor,
-             accumulate: bool = False) -> torch.Tensor:
-    """out[t] (+)= sum_r weights[t, r] W_down[ids[t, r]] y[t, r]; w_down [experts, N, F]; out float32 [T, N]."""
+             accumulate: bool = False, ws=None) -> torch.Tensor:
+    """out[t] (+)= sum_r weights[t, r] W_down[ids[t, r]] y[t, r]; w_down [experts, N, F]; out float32 [T, N].  Every pair's
+    row first (32-bit, in a buffer of the workspace `ws` when given), then the weighted sum per token: two launches."""
     _cuda(y, ids, weights, w_down, out)
     T, top, F = y.shape
     E, N, _ = w_down.shape
     assert y.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, N, F) and out.shape == (T, N)
     assert out.dtype == torch.float32 and out.is_contiguous() and ids.shape == (T, top) and weights.shape == (T, top)
-    call("gb_moe_down", ptr(y), dtype_code(y), T, F, N, top, ptr(ids), ptr(weights), ptr(w_down), dtype_code(w_down), ptr(out),
-         int(bool(accumulate)), stream_ptr())
+    z = ws.get("moe.rows", (T * top, N), torch.float32) if ws is not None else torch.empty(T * top, N, dtype=torch.float32, device=y.device)
+    call("gb_moe_down", ptr(y), dtype_code(y), T, F, N, top, ptr(ids), ptr(weights), ptr(w_down), dtype_code(w_down), ptr(z),
+         ptr(out), int(bool(accumulate)), stream_ptr())
     return out
 
 

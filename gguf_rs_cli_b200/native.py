@@ -155,7 +155,7 @@ _SIGNATURES = {
     "gb_moe_router": [_P, _I, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "gb_moe_route": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "gb_moe_gate_up": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _I, _P],
-    "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P],
+    "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P],
     "gb_unary_act": [_P, _I, _L, _I, _P],
     "gb_moe_grouped_supported": [_I, _I],
     "gb_moe_grouped_scratch_ints": [_I, _I, _I],
@@ -237,7 +237,7 @@ def library():
 
 _launches = 0
 # kernels launched by one call of an entry point, where that is not one
-KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2, "gb_gla": 2, "gb_moe_grouped": 4}
+KERNELS_PER_CALL = {"gb_short_conv_silu": 2, "gb_delta_rule": 2, "gb_latent_decode": 2, "gb_gla": 2, "gb_moe_grouped": 4, "gb_moe_down": 2}
 
 
 def launch_count() -> int:

@@ -179,6 +179,6 @@ class RoutedExperts(Part):
         else:
             y = ctx.ws.get("moe.units", (T, top, self.F), ctx.dtype)
             kernels.moe_gate_up(h, ids, self.w_gate, self.w_up, float(self.p["limit"]), y)
-            kernels.moe_down(y, ids, weights, self.w_down, out, accumulate=bool(self.shared_ff))
+            kernels.moe_down(y, ids, weights, self.w_down, out, accumulate=bool(self.shared_ff), ws=ctx.ws)
         ctx.mark("experts")
         return out
