@@ -204,7 +204,8 @@ def gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, bias
     S <- diag(alpha) S + k v^T, out = S^T (q q_scale), alpha = sigmoid(a + bias)^(1/tau) per head and key channel.
     q, k [T, heads*dim] and v [T, heads*vdim] are column slices of one buffer; a [T, heads*dim] is the decay's
     projection; out float32 [T, heads*vdim].  Two launches: what does not depend on the state for all tokens at
-    once (into a workspace buffer), then the walk."""
+    once (into a workspace buffer), then the walk; five where a sequence brings more than 256 tokens (its segments of 128
+    are walked side by side, from zero, and again from the states that a short carry gives them)."""
     _cuda(q, k, v, a, bias, state, out)
     T, ld = q.shape[0], q.stride(0)
     assert k.stride(0) == ld and v.stride(0) == ld and q.dtype == k.dtype == v.dtype
@@ -215,9 +216,13 @@ def gla(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, bias
     assert bias.numel() == n_heads * dim and bias.is_contiguous() and tau > 0
     need = native.library().gb_gla_scratch_floats(T, n_heads, dim, vdim)
     scratch = ctx.ws.get("gla.prepared", (need,), torch.float32)
+    seg = native.library().gb_gla_segment_floats(ctx.B, ctx.max_qlen, n_heads, dim, vdim)
+    seg_scratch = ctx.ws.get("gla.segments", (seg,), torch.float32) if seg else None
     call("gb_gla", ptr(q), ptr(k), ptr(v), dtype_code(q), ld, ptr(a), dtype_code(a), a.stride(0), ptr(bias), dtype_code(bias),
          1.0 / float(tau), float(q_scale), ptr(state), ptr(out), out.stride(0), ptr(ctx.cu), ptr(ctx.slots), ptr(ctx.qlens),
-         T, ctx.B, n_heads, dim, vdim, ptr(scratch), stream_ptr())
+         T, ctx.B, n_heads, dim, vdim, ptr(scratch), int(ctx.max_qlen), ptr(seg_scratch), stream_ptr())
+    if seg:
+        native.count_launches(3)
     return out
 
 

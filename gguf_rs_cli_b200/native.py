@@ -150,7 +150,8 @@ _SIGNATURES = {
     "gb_norm_residual_add": [_P, _P, _I, _L, _I, _I, _P, _I, _F, _P, _P],
     "gb_head_prep_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _I, _P, _L, _F, _P, _L, _P, _P, _P,
                               _I, _I, _I, _P, _P, _I, _P],
-    "gb_gla": [_P, _P, _P, _I, _L, _P, _I, _L, _P, _I, _F, _F, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "gb_gla": [_P, _P, _P, _I, _L, _P, _I, _L, _P, _I, _F, _F, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+    "gb_gla_segment_floats": [_I, _I, _I, _I, _I],
     "gb_gla_scratch_floats": [_I, _I, _I, _I],
     "gb_moe_router": [_P, _I, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "gb_moe_route": [_P, _I, _I, _I, _I, _I, _F, _P, _P, _P],
@@ -201,7 +202,7 @@ _SIGNATURES = {
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }
-_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_moe_grouped_scratch_ints": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
+_RESTYPES = {"gb_delta_rule_scratch_floats": ctypes.c_longlong, "gb_gla_scratch_floats": ctypes.c_longlong, "gb_gla_segment_floats": ctypes.c_longlong, "gb_moe_grouped_scratch_ints": ctypes.c_longlong, "gb_latent_decode_scratch_floats": ctypes.c_longlong, "gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:
