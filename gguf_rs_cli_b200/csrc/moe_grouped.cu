@@ -45,7 +45,8 @@ __device__ __forceinline__ int mg_swz(int row, int chunk) { return row * MG_BK +
 // first place in perm), n_tiles [1].  Places inside an expert's range are handed out by atomics on shared memory: their
 // order is not fixed, and nothing depends on it (every pair's rows are computed for themselves).
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ offsets,
-                                                        int* __restrict__ perm, int* __restrict__ tiles, int* __restrict__ n_tiles) {
+                                                        int* __restrict__ perm, int* __restrict__ tiles, int* __restrict__ n_tiles,
+                                                        int* __restrict__ place_of) {
     __shared__ int count[1024], cursor[1024], tile0[1025];
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     __syncthreads();
@@ -70,7 +71,34 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
             tiles[2 * j + 1] = cursor[e] + (j - tile0[e]) * MG_BM;
         }
     __syncthreads();
-    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) perm[atomicAdd(&cursor[ids[i]], 1)] = i;
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int place = atomicAdd(&cursor[ids[i]], 1);
+        perm[place] = i;
+        if (place_of) place_of[i] = place;
+    }
+}
+
+// rows[place, :] = h[perm[place] / top, :]: the tokens' rows in the order of their pairs' experts (16-byte pieces).
+__global__ void moe_gather_rows_kernel(const uint4* __restrict__ h, long long ldh16, const int* __restrict__ perm, int top, int k16,
+                                       uint4* __restrict__ rows, long long total) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long place = i / k16;
+    const int c = int(i - place * k16);
+    rows[i] = h[size_t(perm[place] / top) * ldh16 + c];
+}
+
+// out[t, n] (+)= sum_r weights[t, r] z[place_of[t * top + r], n], the choices in their order.
+__global__ void moe_combine_sorted_kernel(const float* __restrict__ z, const int* __restrict__ place_of,
+                                          const float* __restrict__ weights, int top, int N, float* __restrict__ out, int accumulate,
+                                          long long total) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / N;
+    const int n = int(i - t * N);
+    float acc = 0.f;
+    for (int r = 0; r < top; ++r) acc = fmaf(weights[t * top + r], z[size_t(place_of[t * top + r]) * N + n], acc);
+    out[i] = accumulate ? out[i] + acc : acc;
 }
 
 struct MgParams {
@@ -235,7 +263,7 @@ GB_API int gb_moe_grouped(const void* h, long long ldh, int T, int K, int F, int
     int* perm = offsets + E + 1;
     int* tiles = perm + pairs;
     int* n_tiles = tiles + 2 * max_tiles;
-    moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, pairs, E, offsets, perm, tiles, n_tiles);
+    moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, pairs, E, offsets, perm, tiles, n_tiles, nullptr);
     GB_LAUNCH_OK("gb_moe_grouped (sort)");
     static bool configured = false;
     constexpr int SMEM_GLU = MG_STAGES * (MG_BM + 2 * MG_BN) * MG_BK * 2, SMEM_ONE = MG_STAGES * (MG_BM + MG_BN) * MG_BK * 2;
@@ -259,5 +287,37 @@ GB_API int gb_moe_grouped(const void* h, long long ldh, int T, int K, int F, int
     const long long total = (long long)T * N;
     moe_combine_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(z, weights, top, N, out, accumulate, total);
     GB_LAUNCH_OK("gb_moe_grouped (sum)");
+    return 0;
+}
+
+// The pieces of the path that runs every expert's products as ordinary products over its own rows (the caller reads the
+// experts' offsets on the host and launches them): pairs sorted by expert (offsets [E + 1], perm and place_of [T * top]),
+// the tokens' rows gathered in that order, and at the end the weighted sum per token over rows in that order.
+GB_API int gb_moe_sort(const int* ids, int T, int top, int E, int* offsets, int* perm, int* place_of, int* tiles_scratch,
+                       cudaStream_t stream) {
+    GB_REQUIRE(E > 0 && E <= 1024 && top > 0 && T >= 0, "gb_moe_sort: bad sizes");
+    if (T == 0) return 0;
+    const int pairs = T * top, max_tiles = (pairs + MG_BM - 1) / MG_BM + E;
+    moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, pairs, E, offsets, perm, tiles_scratch, tiles_scratch + 2 * max_tiles, place_of);
+    GB_LAUNCH_OK("gb_moe_sort");
+    return 0;
+}
+
+GB_API int gb_moe_gather_rows(const void* h, long long ldh, int T, int K, int top, const int* perm, void* rows, cudaStream_t stream) {
+    GB_REQUIRE(K % 8 == 0 && ldh % 8 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(rows)) & 15) == 0,
+               "gb_moe_gather_rows: rows of %d bfloat16 entries must be multiples of 16 bytes and aligned", K);
+    if (T == 0) return 0;
+    const long long total = (long long)T * top * (K / 8);
+    moe_gather_rows_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>((const uint4*)h, ldh / 8, perm, top, K / 8, (uint4*)rows, total);
+    GB_LAUNCH_OK("gb_moe_gather_rows");
+    return 0;
+}
+
+GB_API int gb_moe_combine_sorted(const float* z, const int* place_of, const float* weights, int T, int top, int N, float* out,
+                                 int accumulate, cudaStream_t stream) {
+    if (T == 0) return 0;
+    const long long total = (long long)T * N;
+    moe_combine_sorted_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(z, place_of, weights, top, N, out, accumulate, total);
+    GB_LAUNCH_OK("gb_moe_combine_sorted");
     return 0;
 }

@@ -341,6 +341,42 @@ def moe_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     return out
 
 
+def moe_by_expert(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                  w_down: torch.Tensor, limit: float, out: torch.Tensor, ctx, accumulate: bool = False) -> torch.Tensor:
+    """The routed experts of a step of very many tokens as ordinary products, expert by expert, on the tcgen05 product
+    kernels: the pairs sorted by expert and the tokens' rows gathered in that order on the device; the experts' offsets
+    read on the host (one wait per call: such steps are prompts, which no graph captures); per expert gate, up and down
+    over its own rows; the clamped unit over all rows at once; the weighted sum per token in choice order."""
+    _cuda(h, ids, weights, w_gate, w_up, w_down, out)
+    T, K = h.shape
+    E, F, _ = w_gate.shape
+    N, top = w_down.shape[1], ids.shape[1]
+    P = T * top
+    assert h.dtype == torch.bfloat16 and w_gate.dtype == torch.bfloat16 and out.dtype == torch.float32 and out.shape == (T, N)
+    lib = native.library()
+    scratch = ctx.ws.get("moe.sorted", (lib.gb_moe_grouped_scratch_ints(T, top, E),), torch.int32)
+    order = ctx.ws.get("moe.order", (E + 1 + 2 * P,), torch.int32)
+    offsets, perm, place_of = order[:E + 1], order[E + 1:E + 1 + P], order[E + 1 + P:]
+    call("gb_moe_sort", ptr(ids), T, top, E, ptr(offsets), ptr(perm), ptr(place_of), ptr(scratch), stream_ptr())
+    rows = ctx.ws.get("moe.gathered", (P, K), torch.bfloat16)
+    call("gb_moe_gather_rows", ptr(h), h.stride(0), T, K, top, ptr(perm), ptr(rows), stream_ptr())
+    at = offsets.cpu().tolist()
+    gu = ctx.ws.get("moe.gate_up", (P, 2 * F), torch.bfloat16)
+    for e in range(E):
+        a, b = at[e], at[e + 1]
+        if b > a:
+            gemm(rows[a:b], w_gate[e], None, gu[a:b, :F])
+            gemm(rows[a:b], w_up[e], None, gu[a:b, F:])
+    y = glu_clamped(gu, ctx.ws.get("moe.units", (P, F), torch.bfloat16), limit)
+    z = ctx.ws.get("moe.rows", (P, N), torch.float32)
+    for e in range(E):
+        a, b = at[e], at[e + 1]
+        if b > a:
+            gemm(y[a:b], w_down[e], None, z[a:b])
+    call("gb_moe_combine_sorted", ptr(z), ptr(place_of), ptr(weights), T, top, N, ptr(out), int(bool(accumulate)), stream_ptr())
+    return out
+
+
 UNARY_ACTS = {"silu": 1, "gelu_tanh": 2, "gelu": 3}
 
 

@@ -159,6 +159,9 @@ _SIGNATURES = {
     "gb_moe_down": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P],
     "gb_unary_act": [_P, _I, _L, _I, _P],
     "gb_moe_grouped_supported": [_I, _I],
+    "gb_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "gb_moe_gather_rows": [_P, _L, _I, _I, _I, _P, _P, _P],
+    "gb_moe_combine_sorted": [_P, _P, _P, _I, _I, _I, _P, _I, _P],
     "gb_moe_grouped_scratch_ints": [_I, _I, _I],
     "gb_moe_grouped": [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P],
     "gb_glu_clamped": [_P, _L, _P, _I, _I, _I, _F, _P],

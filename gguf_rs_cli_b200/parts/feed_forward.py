@@ -154,6 +154,8 @@ class RoutedExperts(Part):
             self.shared_down = Linear(d, name="moe.shared_down")
 
     TOKEN_BY_TOKEN = 16           # steps of at most this many tokens run every (token, choice) pair for itself
+    BY_EXPERT = 128               # pairs per expert, on average, from which the experts run as ordinary products of their own
+    BY_EXPERT_ENTRIES = 8 << 20   # ... where an expert's matrix has at least this many entries
     graph_class = ()              # grids depend on the number of tokens only
     reads_stream = True           # a block that has the rows in 32-bit gives them too (x32): the router reads those
 
@@ -172,7 +174,14 @@ class RoutedExperts(Part):
                                       float(self.p["shared_limit"]))
             self.shared_down(act, ctx, out_dtype=torch.float32, buffer="moe.out")
             ctx.mark("shared")
-        if T > self.TOKEN_BY_TOKEN and kernels.moe_grouped_supported(h, self.w_gate):
+        if not ctx.decode and T * top >= self.BY_EXPERT * self.n and self.F * E >= self.BY_EXPERT_ENTRIES \
+                and kernels.moe_grouped_supported(h, self.w_gate):
+            # very many tokens (an expert gets 128 rows or more on average) and large experts: every expert's products on
+            # the tcgen05 kernels (8,192 pairs, 16 experts of 3,584 x 4,096: 1.65 against 3.99 ms; of 2,048 x 2,048: 1.17
+            # against 1.21 ms, the launches of small products fill a quarter of the device)
+            kernels.moe_by_expert(h, ids, weights, self.w_gate, self.w_up, self.w_down, float(self.p["limit"]), out, ctx,
+                                  accumulate=bool(self.shared_ff))
+        elif T > self.TOKEN_BY_TOKEN and kernels.moe_grouped_supported(h, self.w_gate):
             # many tokens: pairs sorted by expert on the device, tiles of 64 pairs on the tensor cores
             kernels.moe_grouped(h, ids, weights, self.w_gate, self.w_up, self.w_down, float(self.p["limit"]), out, ctx,
                                 accumulate=bool(self.shared_ff))

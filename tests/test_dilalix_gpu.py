@@ -179,6 +179,11 @@ def test_grouped_experts_agree_with_token_by_token(T, K, F, N, E, top, skew):
     fresh = torch.full((T, N), 9.0, device=DEV)
     kernels.moe_grouped(hd, idd, wtd, wg.to(DEV), wu.to(DEV), wd.to(DEV), limit, fresh, ctx, accumulate=False)
     assert torch.equal(fresh, out - base.to(DEV)) or float((fresh - (out - base.to(DEV))).abs().max()) < 1e-5
+    # expert by expert as ordinary products (the path of very many tokens)
+    each = base.clone().to(DEV)
+    kernels.moe_by_expert(hd, idd, wtd, wg.to(DEV), wu.to(DEV), wd.to(DEV), limit, each, ctx, accumulate=True)
+    assert_close(each - base.to(DEV), want.float(), "bfloat16", "expert by expert")
+    assert float((each - one).abs().max()) <= 2e-2 * float(want.abs().max())
 
 
 @pytest.mark.parametrize("D,Dv,H,cuts", [(8, 4, 1, None), (24, 40, 3, None), (64, 64, 2, None), (100, 36, 2, None), (128, 128, 1, None),
