@@ -386,6 +386,42 @@ def test_long_decoding_through_a_ring_that_goes_round(name, dtype):
     settle(tally, f"{name} long decoding")
 
 
+@pytest.mark.parametrize("kind", ["gla", "attention", "bare"])
+def test_models_of_one_kind_of_layer(kind):
+    """A model whose layers are all gated linear attention keeps no keys at all (a cache without page groups); one of
+    attention alone keeps no fixed-size state of a mixer; `bare` has one attention layer with nothing optional: no window,
+    no rotation, no mixing of values, as many key/value heads as heads, values as wide as keys, no feed-forward."""
+    from gguf_rs_cli_b200.engine.step import Engine
+    cfg = copy.deepcopy(CONFIGS["small"][0])
+    if kind == "gla":
+        cfg["layers"] = [cfg["layers"][0], copy.deepcopy(cfg["layers"][0])]
+        cfg["layers"][1]["mixer"]["tau"], cfg["layers"][1]["mlp"] = 2.5, None
+        ranks = {0: 12, 1: 5}
+    elif kind == "attention":
+        cfg["layers"], ranks = cfg["layers"][1:], {}
+    else:
+        cfg["layers"], ranks = [{"type": "attention", "mixer": {"heads": 3, "dim": 24}, "mlp": None}], {}
+    from tests.dilalix_util import make_weights
+    w = make_weights(cfg, ranks, seed=4) if kind != "bare" else make_weights(
+        {**cfg, "layers": [{"type": "attention", "mixer": {"heads": 3, "kv_heads": 3, "dim": 24, "vdim": 24}, "mlp": None}]}, ranks, seed=4)
+    if kind == "bare":
+        del w["l0.mix.vmix"]
+    n = 90
+    toks = torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(9)).tolist()
+    plain_cfg = cfg if kind != "bare" else {**cfg, "layers": [{"type": "attention", "mlp": None, "mixer": {
+        "heads": 3, "kv_heads": 3, "dim": 24, "vdim": 24, "scale": 24 ** -0.5, "v_mix": False, "mask": {"size": 10 ** 9, "keep_first": 0},
+        "rot": {"base": 1.0, "dims": 0}}}]}
+    want = P.forward(plain_cfg, w, toks).float()
+    model = build(cfg, w, "float32").model
+    eng = Engine(model, n_tokens=512, n_slots=2)
+    assert (len(eng.cache.groups) == 0) == (kind == "gla")
+    s = eng.open()
+    got = [eng.step([entry(s, toks[:70], range(70))])]
+    got += [eng.step([entry(s, [toks[i]], [0])]).clone() for i in range(70, n)]
+    eng.close(s)
+    assert_close(torch.cat(got), want, "float32", f"a model of {kind} layers")
+
+
 # ------------------------------------------------- keys that stand out at every edge
 SPIKE = {
     "architecture": "Dilalix", "vocab": 2048, "width": 48, "norm": {"eps": 1e-6},
