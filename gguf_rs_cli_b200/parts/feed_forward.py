@@ -94,7 +94,7 @@ class PlainMLP(Part):
     graph_class = ()
 
     def forward(self, h, ctx: StepContext) -> torch.Tensor:
-        act = kernels.unary_act_(self.up(h, ctx), self.activation)
+        act = self.up(h, ctx, activation=self.activation)
         ctx.mark("up")
         term = self.down(act, ctx, out_dtype=torch.float32)
         ctx.mark("down")

@@ -77,6 +77,18 @@ def test_norm_of_a_result_into_the_stream(E, y_dtype):
     assert torch.equal(xb.cpu(), xd.cpu().to(torch.bfloat16)) and torch.allclose(xd.cpu(), want, rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("act", ["gelu", "silu", "gelu_tanh"])
+def test_activation_of_a_whole_buffer(act):
+    from gguf_rs_cli_b200 import kernels
+    z = torch.randn(37, 50, generator=torch.Generator().manual_seed(3)) * 3
+    want = {"gelu": P.gelu_erf, "silu": P.silu,
+            "gelu_tanh": lambda v: 0.5 * v * (1 + torch.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))}[act](z.double())
+    got = kernels.unary_act_(z.clone().to(DEV), act)
+    assert torch.allclose(got.cpu().double(), want, rtol=1e-5, atol=1e-6)
+    got = kernels.unary_act_(z.to(torch.bfloat16).to(DEV), act)
+    assert float((got.float().cpu().double() - want).abs().max()) <= 4e-2 * float(want.abs().max())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_each_mixer_alone_in_an_unequal_batch(name, dtype):
